@@ -1,6 +1,7 @@
 from .errors import CacheError, ConfigError, WeightsError
 from .fegidra import FegidraConfig
+from .fudelorn import FudelornConfig
 from .llama import Llama3RopeScaling, LlamaConfig
 from .pozirax import PoziraxConfig
 
-__all__ = ["CacheError", "ConfigError", "WeightsError", "FegidraConfig", "Llama3RopeScaling", "LlamaConfig", "PoziraxConfig"]
+__all__ = ["CacheError", "ConfigError", "WeightsError", "FegidraConfig", "FudelornConfig", "Llama3RopeScaling", "LlamaConfig", "PoziraxConfig"]

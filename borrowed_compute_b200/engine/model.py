@@ -36,6 +36,9 @@ class DecoderModel:
         self.final_norm = _build(NORMS, spec.final_norm)
         self.head = _build(HEADS, spec.head)
         self.rt: Optional[Runtime] = None
+        # For looking inside a step: called as after_run(schedule entry, residual) when a run has added to the stream
+        # (an eager step only; a captured step replays without it).
+        self.after_run = None
 
     def named_parts(self):
         """(tensor-name prefix, part) of every part of the model; each block lists its own."""
@@ -93,6 +96,8 @@ class DecoderModel:
             if run.enter is not None:
                 self.junctions[run.enter[0]].forward(residual, embedded, ctx, run.enter[1])
             self.blocks[run.layer].forward(residual, ctx, cache.memory(i), rt)
+            if self.after_run is not None and not ctx.extras.get("graph"):
+                self.after_run(i, residual)
         h = torch.empty((n_want, self.spec.hidden_size), dtype=rt.dtype, device=rt.device)
         self.final_norm.forward(residual, h, want_rows)
         scores = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=rt.device)

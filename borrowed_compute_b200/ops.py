@@ -148,6 +148,8 @@ _CLASS_OF = {
     "bc_moe_product": "expert product", "bc_gemm_tc_grouped": "expert product", "bc_moe_route": "routing", "bc_moe_plan": "expert sort",
     "bc_moe_gather": "expert gather", "bc_moe_combine": "expert sum", "bc_softcap": "softcap", "bc_reentry": "re-entry",
     "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
+    "bc_latent_prepare": "latent norm + append", "bc_latent_query": "latent query", "bc_latent_rows": "attention", "bc_latent_tiles": "attention",
+    "bc_latent_values": "latent values", "bc_norm_add": "norm", "bc_relu2": "activation", "bc_gated_add": "gated sum", "bc_moe_table_route": "routing",
 }
 
 
@@ -998,6 +1000,152 @@ def moe_combine(y: torch.Tensor, choice: torch.Tensor, place: torch.Tensor, weig
         raise KernelError(f"moe_combine: y {tuple(y.shape)} and residual {tuple(residual.shape)} do not fit")
     _call(_fn("bc_moe_combine"), _ptr(y), _ptr(choice), _ptr(place), _ptr(weight), _ptr(residual), _c_int(rows), _c_int(residual.shape[1]),
           _c_int(top), _c_int(1 if weight_on_output else 0), _stream())
+
+
+# ---------------------------------------------------------------------------- latent attention
+
+def latent_prepare(proj: torch.Tensor, q_rank: int, kv_at: int, kv_rank: int, rot: int, gate_at: int, heads: int, q_weight: torch.Tensor,
+                   kv_weight: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor], row_pos: torch.Tensor, row_slot: torch.Tensor,
+                   page_table: Optional[torch.Tensor], c_pages: Optional[torch.Tensor], r_pages: Optional[torch.Tensor], cq: torch.Tensor,
+                   gate: torch.Tensor, eps: float, write_cache: bool = True) -> None:
+    """From a row of the fused down projection ``proj`` (float32: ``q_rank`` values at 0; at ``kv_at`` ``kv_rank`` values and
+    ``rot`` more, unless ``kv_at`` < 0; ``heads`` values at ``gate_at``): cq = RMS norm of the first part times ``q_weight`` in cq's
+    type; the RMS norm of the second part times ``kv_weight`` and the ``rot`` values rotated by the row's position (pairs
+    (i, i + rot / 2), ``cos_sin`` [positions, rot / 2, 2]) into the row's place of ``c_pages`` [pages, 1, 64, kv_rank] and ``r_pages``
+    [pages, 1, 64, rot]; gate = sigmoid of the third part (float32).  Rows whose slot is negative write nothing into the cache."""
+    _need(proj, "proj", torch.float32)
+    _need(cq, "cq")
+    _need(gate, "gate", torch.float32)
+    _need(q_weight, "q_weight", torch.float32)
+    rows, P = proj.shape
+    writes = kv_at >= 0 and write_cache
+    if tuple(cq.shape) != (rows, q_rank) or tuple(gate.shape) != (rows, heads) or q_weight.numel() != q_rank:
+        raise KernelError(f"latent_prepare: proj {tuple(proj.shape)}, cq {tuple(cq.shape)}, gate {tuple(gate.shape)} do not fit")
+    n_pages = max_pages = 0
+    if writes:
+        _need(c_pages, "c_pages", cq.dtype)
+        _need(kv_weight, "kv_weight", torch.float32)
+        _need(page_table, "page_table", torch.int32)
+        n_pages, max_pages = c_pages.shape[0], page_table.shape[1]
+        if c_pages.shape[-1] != kv_rank or c_pages.shape[-2] != PAGE or kv_weight.numel() != kv_rank:
+            raise KernelError(f"latent_prepare: pages of {tuple(c_pages.shape)} do not hold latents of {kv_rank}")
+        if rot > 0:
+            _need(r_pages, "r_pages", cq.dtype)
+            _need(cos_sin, "cos_sin", torch.float32)
+            if r_pages.shape[-1] != rot or r_pages.shape[0] != n_pages or cos_sin.shape[1] * 2 != rot:
+                raise KernelError(f"latent_prepare: rotated keys of {rot} do not fit pages {tuple(r_pages.shape)} or a table of {tuple(cos_sin.shape)}")
+        _bounds_paged("latent_prepare", rows, row_pos, row_slot, page_table, n_pages)
+        if rot > 0:
+            _bounds("latent_prepare: row_pos", row_pos, cos_sin.shape[0], rows)
+    _call(_fn("bc_latent_prepare_" + _suffix(cq.dtype)), _ptr(proj), _c_int(rows), _c_int(P), _c_int(q_rank), _c_int(kv_at), _c_int(kv_rank), _c_int(rot),
+          _c_int(gate_at), _c_int(heads), _ptr(q_weight), _ptr(kv_weight), _ptr(cos_sin), _c_int(0 if cos_sin is None else cos_sin.shape[0]), _ptr(row_pos),
+          _ptr(row_slot), _ptr(page_table), _c_int(max_pages), _c_int(n_pages), _ptr(c_pages if writes else None), _ptr(r_pages if writes else None),
+          _ptr(cq), _ptr(gate), _c_float(eps), _c_int(1 if writes else 0), _stream())
+
+
+def latent_query(q: torch.Tensor, w_uk: torch.Tensor, cos_sin: Optional[torch.Tensor], row_pos: torch.Tensor, out: torch.Tensor, heads: int, dim: int,
+                 rot: int, kv_rank: int) -> None:
+    """out[r, n] = [Wuk_n^T q_n | rot(qr_n)]: q float32 [rows, heads * (dim + rot)], head by head ``dim`` plain values then ``rot``
+    rotated ones; ``w_uk`` [heads * dim, kv_rank]; out [rows, heads, kv_rank + rot] in w_uk's type."""
+    _need(q, "q", torch.float32)
+    _need(w_uk, "w_uk")
+    _need(out, "out", w_uk.dtype)
+    rows = q.shape[0]
+    if q.shape[1] != heads * (dim + rot) or tuple(w_uk.shape) != (heads * dim, kv_rank) or out.numel() != rows * heads * (kv_rank + rot):
+        raise KernelError(f"latent_query: q {tuple(q.shape)}, w_uk {tuple(w_uk.shape)}, out {tuple(out.shape)} do not fit")
+    if rot > 0:
+        _need(cos_sin, "cos_sin", torch.float32)
+        _bounds("latent_query: row_pos", row_pos, cos_sin.shape[0], rows)
+    _call(_fn("bc_latent_query_" + _suffix(w_uk.dtype)), _ptr(q), _ptr(w_uk), _ptr(cos_sin if rot > 0 else None),
+          _c_int(cos_sin.shape[0] if rot > 0 else 0), _ptr(row_pos), _ptr(out), _c_int(rows), _c_int(heads), _c_int(dim), _c_int(rot), _c_int(kv_rank), _stream())
+
+
+LATENT_MAX_RANK, LATENT_MAX_ROT = 512, 128
+
+
+def latent_rows(a: torch.Tensor, c_pages: torch.Tensor, r_pages: Optional[torch.Tensor], page_table: torch.Tensor, row_pos: torch.Tensor,
+                row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_rank: int, rot: int, window: int, scale: float) -> None:
+    """Attention over cached latents, one warp a (row, head): a [rows, heads, kv_rank + rot] are the absorbed queries, every head
+    reads the same ``c_pages`` [pages, 1, 64, kv_rank] (keys and values at once) and ``r_pages`` [pages, 1, 64, rot];
+    out [rows, heads, kv_rank] = sum_j softmax_j((a_c . c_j + a_r . r_j) * scale) c_j over the positions j the row sees
+    (``window`` > 0: the last ``window`` ones, itself included).  Rows whose slot is negative give zeros."""
+    _need(a, "a")
+    _need(c_pages, "c_pages", a.dtype)
+    _need(out, "out", a.dtype)
+    _need(page_table, "page_table", torch.int32)
+    rows = a.shape[0]
+    if a.numel() != rows * heads * (kv_rank + rot) or out.numel() != rows * heads * kv_rank or c_pages.shape[-1] != kv_rank:
+        raise KernelError(f"latent_rows: a {tuple(a.shape)}, out {tuple(out.shape)}, pages {tuple(c_pages.shape)} do not fit")
+    if rot > 0:
+        _need(r_pages, "r_pages", a.dtype)
+    _bounds_paged("latent_rows", rows, row_pos, row_slot, page_table, c_pages.shape[0])
+    _call(_fn("bc_latent_rows_" + _suffix(a.dtype)), _ptr(a), _ptr(c_pages), _ptr(r_pages if rot > 0 else None), _ptr(page_table), _ptr(row_pos),
+          _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_rank), _c_int(rot), _c_int(page_table.shape[1]), _c_int(c_pages.shape[0]),
+          _c_int(window), _c_float(scale), _stream())
+
+
+def latent_values(ctx: torch.Tensor, w_uv: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, heads: int, kv_rank: int, value_dim: int) -> None:
+    """out[r, n] = gate[r, n] * Wuv_n ctx[r, n]: ctx [rows, heads, kv_rank], ``w_uv`` [heads * value_dim, kv_rank], gate float32
+    [rows, heads], out [rows, heads * value_dim] in ctx's type."""
+    _need(ctx, "ctx")
+    _need(w_uv, "w_uv", ctx.dtype)
+    _need(gate, "gate", torch.float32)
+    _need(out, "out", ctx.dtype)
+    rows = out.shape[0]
+    if ctx.numel() != rows * heads * kv_rank or tuple(w_uv.shape) != (heads * value_dim, kv_rank) or out.shape[1] != heads * value_dim \
+            or gate.numel() != rows * heads:
+        raise KernelError(f"latent_values: ctx {tuple(ctx.shape)}, w_uv {tuple(w_uv.shape)}, out {tuple(out.shape)} do not fit")
+    _call(_fn("bc_latent_values_" + _suffix(ctx.dtype)), _ptr(ctx), _ptr(w_uv), _ptr(gate), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_rank),
+          _c_int(value_dim), _stream())
+
+
+# ------------------------------------------------------------- norms after a sublayer, relu squared
+
+def norm_add(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, eps: float) -> None:
+    """residual[r] += y[r] * rsqrt(mean(y[r]^2) + eps) * weight for the rows of y; all float32."""
+    _need(y, "y", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(residual, "residual", torch.float32)
+    rows, E = y.shape
+    if residual.shape[0] < rows or residual.shape[1] != E or weight.numel() != E:
+        raise KernelError(f"norm_add: y {tuple(y.shape)}, residual {tuple(residual.shape)}, weight {weight.numel()} do not fit")
+    _call(_fn("bc_norm_add_f32"), _ptr(y), _ptr(weight), _ptr(residual), _c_int(rows), _c_int(E), _c_float(eps), _stream())
+
+
+def relu2(z: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(z, 0)^2: z float32, out of any type the kernels know, the same shape."""
+    _need(z, "z", torch.float32)
+    _need(out, "out")
+    if out.shape != z.shape:
+        raise KernelError(f"relu2: z {tuple(z.shape)} and out {tuple(out.shape)} differ")
+    _call(_fn("bc_relu2_" + _suffix(out.dtype)), _ptr(z), _ptr(out), ctypes.c_longlong(z.numel()), _stream())
+
+
+def gated_add(h: torch.Tensor, g: torch.Tensor, y: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[r] += sigmoid(g . h[r]) * y[r]: h [rows, K] and g [K] of one type, y and residual float32 [rows, E]."""
+    _need(h, "h")
+    _need(g, "g", h.dtype)
+    _need(y, "y", torch.float32)
+    _need(residual, "residual", torch.float32)
+    rows, K = h.shape
+    if g.numel() != K or y.shape[0] != rows or residual.shape[0] < rows or residual.shape[1] != y.shape[1]:
+        raise KernelError(f"gated_add: h {tuple(h.shape)}, g {g.numel()}, y {tuple(y.shape)}, residual {tuple(residual.shape)} do not fit")
+    _call(_fn("bc_gated_add_" + _suffix(h.dtype)), _ptr(h), _ptr(g), _ptr(y), _ptr(residual), _c_int(rows), _c_int(K), _c_int(y.shape[1]), _stream())
+
+
+def moe_table_route(table: torch.Tensor, tokens: torch.Tensor, row_slot: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor,
+                    experts: int) -> None:
+    """choice[r] = table[tokens[r]] ([vocabulary, top] int32), weight = 1 / top: the experts of a row are named by its token id.
+    Rows whose slot is negative, and entries outside the experts, choose nothing (-1)."""
+    _need(table, "table", torch.int32)
+    _need(tokens, "tokens", torch.int32)
+    _need(choice, "choice", torch.int32)
+    _need(weight, "weight", torch.float32)
+    rows, top = choice.shape
+    if table.shape[1] != top or tokens.numel() < rows or weight.shape != choice.shape:
+        raise KernelError(f"moe_table_route: table {tuple(table.shape)}, choice {tuple(choice.shape)} do not fit")
+    _call(_fn("bc_moe_table_route"), _ptr(table), _ptr(tokens), _ptr(row_slot), _ptr(choice), _ptr(weight), _c_int(rows), _c_int(table.shape[0]),
+          _c_int(experts), _c_int(top), _stream())
 
 
 # ----------------------------------------------------------------------- the stream and the scores

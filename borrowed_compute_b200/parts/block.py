@@ -7,7 +7,10 @@ The parallel block: x += mixer(conv(norm1(x))) + feed_forward(norm2(x)), both br
 the same x, the mixer's input first passing a short causal convolution over time whose last
 inputs are per-sequence state.  The feed-forward (and its norm) may be left out; a feed-forward
 without a norm of its own reads what the mixer reads, x += mixer(h) + feed_forward(h) with
-h = norm1(x)."""
+h = norm1(x).
+
+The sandwich block: a norm before and after each sublayer, x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))).
+The second half may be left out."""
 
 from __future__ import annotations
 
@@ -83,3 +86,33 @@ class ParallelBlock(Block):
         self.mixer.forward(h, residual, ctx, mem)
         if self.feed_forward is not None:
             self.feed_forward.forward(h if h2 is None else h2, residual, ctx)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """Every sublayer's result passes a norm of its own before it joins the stream, so no product can add into the stream
+    itself: the sublayer adds into a cleared float buffer, and one kernel norms that and adds it."""
+
+    ROLES = {"norm1": NORMS, "mixer": MIXERS, "norm1b": NORMS, "norm2": NORMS, "feed_forward": FEED_FORWARDS, "norm2b": NORMS}
+    OPTIONAL = ("norm2", "feed_forward", "norm2b")
+
+    def __init__(self, parts, hidden_size: int):
+        super().__init__(parts, hidden_size)
+        if len({self.norm2 is None, self.feed_forward is None, self.norm2b is None}) != 1:
+            raise ValueError("a sandwich block has a feed-forward with both of its norms, or none of the three")
+        for role in ("norm1b", "norm2b"):
+            if getattr(self, role) is not None and type(getattr(self, role)) is not RMSNorm:
+                raise ValueError(f"the norm after a sublayer ('{role}') must be a plain RMS norm")
+
+    def forward(self, residual: torch.Tensor, ctx: StepContext, mem: RunMemory, rt: Runtime) -> None:
+        rows = residual.shape[0]
+        h = torch.empty((rows, self.hidden_size), dtype=rt.dtype, device=residual.device)
+        y = torch.zeros((rows, self.hidden_size), dtype=torch.float32, device=residual.device)
+        self.norm1.forward(residual, h)
+        self.mixer.forward(h, y, ctx, mem)
+        ops.norm_add(y, self.norm1b.weight, residual, self.norm1b.eps)
+        if self.feed_forward is not None:
+            y.zero_()
+            self.norm2.forward(residual, h)
+            self.feed_forward.forward(h, y, ctx)
+            ops.norm_add(y, self.norm2b.weight, residual, self.norm2b.eps)

@@ -38,3 +38,35 @@ class SwiGLU(FeedForward):
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         products.linear(x, self.w_gate_up, h, products.EPI_SWIGLU, "gate/up product")
         products.linear(h, self.w_down, residual, products.EPI_ADD_F32, "down product")
+
+
+@FEED_FORWARDS.register("plain_mlp")
+class PlainMLP(FeedForward):
+    """down( act(up x) ) without a gate; ``activation``: "relu2", the square of relu.  The up product keeps its float sums, the
+    activation rounds once.  ``up`` and ``down`` are the names the matrices carry after the part's prefix."""
+
+    ACTIVATIONS = ("relu2",)
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu2", up: str = "up", down: str = "down"):
+        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, activation=activation, up=up, down=down)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not known (known: {list(self.ACTIVATIONS)})")
+        self.hidden_size, self.intermediate_size, self.activation = int(hidden_size), int(intermediate_size), activation
+        self.names = (str(up), str(down))
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        e, f = self.hidden_size, self.intermediate_size
+        return {self.names[0]: TensorSpec((f, e)), self.names[1]: TensorSpec((e, f))}
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().load(tensors, rt)
+        self.w_up, self.w_down = tensors[self.names[0]].contiguous(), tensors[self.names[1]].contiguous()
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        from .. import ops
+
+        z = torch.empty((x.shape[0], self.intermediate_size), dtype=torch.float32, device=x.device)
+        products.linear(x, self.w_up, z, products.EPI_STORE_F32, "up product")
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+        ops.relu2(z, act)
+        products.linear(act, self.w_down, residual, products.EPI_ADD_F32, "down product")

@@ -49,36 +49,88 @@ def _llama3_rule(d: Mapping[str, Any]) -> Callable[[float], float]:
     return lambda f: llama3_scaled_frequency(f, factor, low, high, orig)
 
 
+def yarn_ramp(dims: int, theta: float, original: float, fast: float, slow: float):
+    """pair index -> share of the slowed frequency: 0 for pairs whose wave turns more than ``fast`` times within ``original``
+    positions, 1 for those that turn fewer than ``slow`` times, linear in the pair's index between the two (the index at which a
+    wave turns t times is dims ln(original / (2 pi t)) / (2 ln theta), rounded down for ``fast`` and up for ``slow``)."""
+    def turns(t: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(turns(fast)), 0)
+    hi = min(math.ceil(turns(slow)), dims - 1)
+    return lambda i: min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+
+
+def _yarn_numbers(d: Mapping[str, Any]):
+    try:
+        factor, original, fast, slow = float(d["factor"]), float(d["original"]), float(d["fast"]), float(d["slow"])
+    except (KeyError, TypeError, ValueError) as e:
+        raise ValueError(f"yarn frequency scaling needs factor, original, fast and slow as numbers, got {dict(d)!r}") from e
+    if factor <= 0 or original <= 0 or fast <= 0 or slow <= 0:
+        raise ValueError(f"yarn frequency scaling values must be positive: {dict(d)!r}")
+    return factor, original, fast, slow
+
+
+def _yarn_rule(d: Mapping[str, Any], head_dim: int, theta: float) -> Callable[[float, int], float]:
+    """f_i -> f_i / factor * ramp_i + f_i * (1 - ramp_i); the rule's numbers: factor, original (positions), fast, slow (turns)."""
+    factor, original, fast, slow = _yarn_numbers(d)
+    ramp = yarn_ramp(head_dim, theta, original, fast, slow)
+    return lambda f, i: f / factor * ramp(i) + f * (1.0 - ramp(i))
+
+
+def _yarn_magnitude(d: Mapping[str, Any]) -> float:
+    return 0.1 * math.log(_yarn_numbers(d)[0]) + 1.0
+
+
 # Rules that rescale rotary frequencies, by the name a configuration gives them.  Each takes
 # the rule's own numbers (a plain mapping) and returns frequency -> frequency.
 FREQUENCY_SCALINGS: Dict[str, Callable[[Mapping[str, Any]], Callable[[float], float]]] = {"llama3": _llama3_rule}
+# Rules that also need to know which pair a frequency belongs to: (numbers, rotated dimensions, theta) -> ((frequency, pair) ->
+# frequency).  And, by the same names, the factor such a rule puts on every cosine and sine of the table (none: 1).
+INDEXED_SCALINGS: Dict[str, Callable[[Mapping[str, Any], int, float], Callable[[float, int], float]]] = {"yarn": _yarn_rule}
+TABLE_MAGNITUDES: Dict[str, Callable[[Mapping[str, Any]], float]] = {"yarn": _yarn_magnitude}
 
 
-def frequency_rule(scaling: Optional[Mapping[str, Any]]) -> Optional[Callable[[float], float]]:
+def frequency_rule(scaling: Optional[Mapping[str, Any]], head_dim: int = 0, theta: float = 0.0) -> Optional[Callable[[float, int], float]]:
+    """(frequency, pair index) -> frequency for the rule a configuration names, or None."""
     if scaling is None:
         return None
     kind = scaling.get("rope_type", scaling.get("type"))
+    if kind in INDEXED_SCALINGS:
+        return INDEXED_SCALINGS[kind](scaling, head_dim or 2, theta or 10000.0)
     if kind not in FREQUENCY_SCALINGS:
-        raise ValueError(f"rotary frequency scaling {kind!r} is not known (known: {sorted(FREQUENCY_SCALINGS)})")
-    return FREQUENCY_SCALINGS[kind](scaling)
+        raise ValueError(f"rotary frequency scaling {kind!r} is not known (known: {sorted(set(FREQUENCY_SCALINGS) | set(INDEXED_SCALINGS))})")
+    rule = FREQUENCY_SCALINGS[kind](scaling)
+    return lambda f, i: rule(f)
+
+
+def table_magnitude(scaling: Optional[Mapping[str, Any]]) -> float:
+    """The factor on every cosine and sine that the configuration's rule asks for (1 for most)."""
+    if scaling is None:
+        return 1.0
+    kind = scaling.get("rope_type", scaling.get("type"))
+    return float(TABLE_MAGNITUDES[kind](scaling)) if kind in TABLE_MAGNITUDES else 1.0
 
 
 def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[Mapping[str, Any]]) -> torch.Tensor:
     """float32 [head_dim // 2]: radians per position of each rotated pair; ``scaling`` is
     a mapping {"rope_type": name, ...the rule's numbers} or None."""
-    rule = frequency_rule(scaling)
+    rule = frequency_rule(scaling, head_dim, theta)
     out = []
     for i in range(head_dim // 2):
         f = float(theta) ** (-2.0 * i / head_dim)
-        out.append(f if rule is None else rule(f))
+        out.append(f if rule is None else rule(f, i))
     return torch.tensor(out, dtype=torch.float64).to(torch.float32)
 
 
-def rotary_table(inv_freq: torch.Tensor, positions: int) -> torch.Tensor:
-    """float32 [positions, pairs, 2] of (cos, sin) of float32(position) * inv_freq."""
+def rotary_table(inv_freq: torch.Tensor, positions: int, magnitude: float = 1.0) -> torch.Tensor:
+    """float32 [positions, pairs, 2] of (cos, sin) of float32(position) * inv_freq, times ``magnitude``."""
     pos = torch.arange(positions, dtype=torch.float32)
     angle = (pos[:, None] * inv_freq[None, :].to(torch.float32)).to(torch.float64)
-    return torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).to(torch.float32).contiguous()
+    table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1)
+    if magnitude != 1.0:
+        table = table * float(magnitude)
+    return table.to(torch.float32).contiguous()
 
 
 _tables: Dict[Tuple, RotaryTable] = {}
@@ -95,7 +147,7 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"rotary encoding needs an even head size, got {head_dim}")
         self.head_dim, self.theta, self.pairing, self.max_positions = int(head_dim), float(theta), pairing, int(max_positions)
         self.scaling = None if scaling is None else dict(scaling)
-        frequency_rule(self.scaling)   # refuses an unknown or inconsistent rule when the part is built
+        frequency_rule(self.scaling, self.head_dim, self.theta)   # refuses an unknown or inconsistent rule when the part is built
         self._table: Optional[RotaryTable] = None
 
     def load(self, tensors, rt: Runtime) -> None:
@@ -104,7 +156,7 @@ class RotaryEncoding(PositionEncoding):
         key = (self.head_dim, self.theta, self.pairing, None if self.scaling is None else tuple(sorted(self.scaling.items())),
                positions, str(rt.device))
         if key not in _tables:
-            table = rotary_table(inverse_frequencies(self.head_dim, self.theta, self.scaling), positions)
+            table = rotary_table(inverse_frequencies(self.head_dim, self.theta, self.scaling), positions, table_magnitude(self.scaling))
             _tables[key] = RotaryTable(cos_sin=table.to(rt.device), pairing=PAIRINGS[self.pairing])
         self._table = _tables[key]
 

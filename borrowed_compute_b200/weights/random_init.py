@@ -111,10 +111,31 @@ def _normal_on_device(shape, key: int, dtype: torch.dtype, device) -> torch.Tens
     return out
 
 
+def _distinct_rows(name: str, spec: TensorSpec, seed: int, below: int) -> torch.Tensor:
+    """An int32 table [rows, n] whose rows each hold n different numbers below ``below``: row r starts at a number drawn
+    from (seed, name, r) and steps by another that has no common factor with ``below``."""
+    rows, n = spec.shape
+    if n > below:
+        raise ValueError(f"{name}: {n} different numbers below {below} do not exist")
+    key = np.uint64(tensor_key(seed, name))
+    with np.errstate(over="ignore"):
+        z = key + (np.arange(rows, dtype=np.uint64) + np.uint64(1)) * np.uint64(0x9E3779B97F4A7C15)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    first = (z % np.uint64(below)).astype(np.int64)
+    steps = [s for s in range(1, below + 1) if np.gcd(s, below) == 1]
+    step = np.asarray(steps, dtype=np.int64)[((z >> np.uint64(32)) % np.uint64(len(steps))).astype(np.int64)]
+    table = (first[:, None] + step[:, None] * np.arange(n, dtype=np.int64)[None, :]) % below
+    return torch.from_numpy(table.astype(np.int32))
+
+
 def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype, device: torch.device | str = "cpu") -> torch.Tensor:
     """One tensor's values: drawn in float32, then rounded to ``dtype``; the same bits
     whether ``device`` is the host or a CUDA device."""
     if spec.role == "index":
+        if spec.init.startswith("distinct:"):
+            return _distinct_rows(name, spec, seed, int(spec.init.split(":")[1])).to(device)
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     if spec.init == "ones":
         return torch.ones(spec.shape, dtype=dtype, device=device)
