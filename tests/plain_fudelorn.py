@@ -160,3 +160,145 @@ def forward(config, tensors, tokens, taps=None):
         if taps is not None:
             taps.append(x.copy())
     return rms_norm(x, tensors["final.norm"], eps) @ np.asarray(tensors["head"], dtype=np.float64).T
+
+
+# ------------------------------------------------------------------------------ small models for the tests
+
+def _rot(dims, base, scaling=None):
+    out = {"base": base, "dims": dims}
+    if scaling:
+        out["scaling"] = scaling
+    return out
+
+
+def _windowed(heads, dim, vdim, q_rank, kv_rank, window, scale=None):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "mask": {"size": window}}
+    m["scale"] = scale if scale is not None else 1.0 / math.sqrt(dim)
+    return m
+
+
+def _rotated(heads, dim, vdim, q_rank, kv_rank, rot_dim, base, scaling=None, kv_from=None, scale=None):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "rot_dim": rot_dim, "rot": _rot(rot_dim, base, scaling)}
+    m["scale"] = scale if scale is not None else 1.0 / math.sqrt(dim + rot_dim)
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _moe(experts, top, ff, shared_ff=0):
+    out = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared_ff:
+        out["shared"] = {"ff": shared_ff}
+    return out
+
+
+# A: windows of 5 and 70 positions (inside a page and across a page's border), a stretched rotation that the tests'
+# positions pass, a layer that reads another's cache and has no feed-forward, three experts a token.
+SMALL_A = {
+    "architecture": "Fudelorn", "vocab": 160, "width": 96, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "latent_attention_2", "mixer": _windowed(3, 16, 24, 40, 48, 5), "mlp": {"kind": "dense", "ff": 176}},
+        {"type": "latent_attention", "mixer": _rotated(2, 32, 16, 64, 72, 8, 10000.0, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}),
+         "mlp": _moe(5, 3, 40, shared_ff=56)},
+        {"type": "latent_attention_2", "mixer": _windowed(5, 8, 8, 24, 32, 70, scale=0.5), "mlp": _moe(4, 2, 48)},
+        {"type": "latent_attention", "mixer": _rotated(4, 24, 40, 32, 72, 8, 10000.0, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}, kv_from=1),
+         "mlp": None},
+    ],
+}
+# B: one head, one expert a token, a window of one position (a row sees itself alone), a latent whose width is no
+# multiple of eight, a rotation without a stretch, a window exactly a page long.
+SMALL_B = {
+    "architecture": "Fudelorn", "vocab": 97, "width": 64, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "latent_attention", "mixer": _rotated(1, 16, 16, 16, 36, 4, 500000.0, scale=0.3), "mlp": _moe(3, 1, 32, shared_ff=16)},
+        {"type": "latent_attention_2", "mixer": _windowed(2, 12, 20, 8, 20, 1), "mlp": {"kind": "dense", "ff": 72}},
+        {"type": "latent_attention_2", "mixer": _windowed(4, 16, 8, 32, 64, 64), "mlp": {"kind": "dense", "ff": 40}},
+    ],
+}
+SMALL = {"A": SMALL_A, "B": SMALL_B}
+
+
+def to_bf16(a):
+    """Rounds float values to the nearest bfloat16 (ties to even), kept as float32."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32)
+
+
+def make_weights(config, seed, spread=1.0):
+    """Seeded weights by tensor name, every value a bfloat16 (so that engines of both types hold the same numbers): matrices of
+    spread ``spread`` / sqrt(inputs), norm weights around one, tables whose rows name different experts."""
+    rng = np.random.default_rng(seed)
+    E, V = int(config["width"]), int(config["vocab"])
+
+    def mat(rows, cols, s=spread):
+        return to_bf16(rng.standard_normal((rows, cols)) * s / math.sqrt(cols))
+
+    def vec(n):
+        return to_bf16(1.0 + 0.25 * rng.uniform(-1, 1, n))
+
+    w = {"embed": to_bf16(rng.standard_normal((V, E))), "final.norm": vec(E), "head": mat(V, E)}
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        H, D, DV, R, rot = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m.get("rot_dim", 0)
+        w[p + "norm1"], w[p + "norm1b"] = vec(E), vec(E)
+        w[p + "mix.dq"], w[p + "mix.dq.norm"] = mat(m["q_rank"], E, 2.0 * spread), vec(m["q_rank"])
+        w[p + "mix.uq"] = mat(H * (D + rot), m["q_rank"], 2.0 * spread)
+        if "kv_from" not in m:
+            w[p + "mix.dkv"], w[p + "mix.dkv.norm"] = mat(R + rot, E, 2.0 * spread), vec(R)
+        w[p + "mix.uk"], w[p + "mix.uv"] = mat(H * D, R, 2.0 * spread), mat(H * DV, R)
+        w[p + "mix.g"], w[p + "mix.o"] = mat(H, E, 2.0 * spread), mat(E, H * DV)
+        mlp = layer.get("mlp")
+        if mlp is None:
+            continue
+        w[p + "norm2"], w[p + "norm2b"] = vec(E), vec(E)
+        if mlp["kind"] == "dense":
+            w[p + "mlp.up"], w[p + "mlp.down"] = mat(mlp["ff"], E, 2.0 * spread), mat(E, mlp["ff"])
+            continue
+        n, top = mlp["router"]["experts"], mlp["router"]["top"]
+        for e in range(n):
+            w[p + f"mlp.e{e}.up"], w[p + f"mlp.e{e}.down"] = mat(mlp["expert"]["ff"], E, 2.0 * spread), mat(E, mlp["expert"]["ff"])
+        w[p + "mlp.table"] = np.stack([rng.permutation(n)[:top] for _ in range(V)]).astype(np.int32)
+        if mlp.get("shared"):
+            f = mlp["shared"]["ff"]
+            w[p + "mlp.shared.up"], w[p + "mlp.shared.down"], w[p + "mlp.shared.sg"] = mat(f, E, 2.0 * spread), mat(E, f), mat(1, E, 2.0 * spread)
+    return w
+
+
+def drawn_config(rng):
+    """A configuration with sizes drawn at random: other widths, head counts, layer orders, windows and constants every time."""
+    E = int(rng.choice([32, 48, 80, 128]))
+    layers, owners = [], []
+    for i in range(int(rng.integers(2, 5))):
+        mlp = [None, {"kind": "dense", "ff": int(rng.choice([24, 56, 96]))},
+               _moe(int(rng.integers(2, 7)), 1, int(rng.choice([16, 40])), shared_ff=int(rng.choice([0, 24])))][int(rng.integers(0, 3))]
+        if mlp and mlp["kind"] == "moe":
+            mlp["router"]["top"] = int(rng.integers(1, mlp["router"]["experts"] + 1))
+        H, D, DV = int(rng.integers(1, 6)), int(rng.choice([8, 16, 24, 40])), int(rng.choice([8, 16, 48]))
+        qr, R = int(rng.choice([8, 24, 48])), int(rng.choice([16, 36, 64, 136]))
+        if rng.random() < 0.5:
+            m = _windowed(H, D, DV, qr, R, int(rng.choice([1, 2, 7, 33, 64, 65, 200])), scale=float(rng.uniform(0.1, 0.5)))
+            layers.append({"type": "latent_attention_2", "mixer": m, "mlp": mlp})
+        else:
+            scaling = None if rng.random() < 0.4 else {"factor": float(rng.choice([2.0, 8.0])), "original": int(rng.choice([16, 64])),
+                                                      "fast": float(rng.choice([4.0, 32.0])), "slow": float(rng.choice([0.5, 1.0]))}
+            rot, base = int(rng.choice([2, 4, 8, 16])), float(rng.choice([100.0, 10000.0, 500000.0]))
+            kv_from = None
+            if owners and rng.random() < 0.5:
+                kv_from = int(rng.choice(owners))
+                o = layers[kv_from]["mixer"]
+                R, rot, base, scaling = o["kv_rank"], o["rot_dim"], o["rot"]["base"], o["rot"].get("scaling")
+            m = _rotated(H, D, DV, qr, R, rot, base, scaling, kv_from=kv_from, scale=float(rng.uniform(0.1, 0.5)))
+            layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+            if kv_from is None:
+                owners.append(i)
+    return {"architecture": "Fudelorn", "vocab": int(rng.choice([50, 131, 300])), "width": E, "norm": {"eps": float(rng.choice([1e-5, 1e-6]))},
+            "layers": layers}
+
+
+def generate(config, tensors, prompt, n):
+    """Greedy: the n tokens after ``prompt``, the lowest id winning a tie."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(np.argmax(forward(config, tensors, toks)[-1])))
+    return toks[len(prompt):]

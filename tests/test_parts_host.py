@@ -58,7 +58,7 @@ def test_the_rotary_part_scales_frequencies_as_the_plain_implementation_does():
         lo, hi = (llama3_scaled_frequency(2 * math.pi / (edge * k), 4.0, 1.0, 4.0, 64) * edge * k for k in (1 - 1e-9, 1 + 1e-9))
         assert abs(lo - hi) < 1e-6
     with pytest.raises(ValueError, match="not known"):
-        inverse_frequencies(32, 1e4, {"rope_type": "yarn", "factor": 2.0})
+        inverse_frequencies(32, 1e4, {"rope_type": "dynamic", "factor": 2.0})
     with pytest.raises(ValueError, match="inconsistent"):
         inverse_frequencies(32, 1e4, {"rope_type": "llama3", "factor": 2.0, "low_freq_factor": 4.0, "high_freq_factor": 1.0,
                                       "original_max_position_embeddings": 64})
