@@ -148,7 +148,8 @@ _CLASS_OF = {
     "bc_moe_product": "expert product", "bc_gemm_tc_grouped": "expert product", "bc_moe_route": "routing", "bc_moe_plan": "expert sort",
     "bc_moe_gather": "expert gather", "bc_moe_combine": "expert sum", "bc_softcap": "softcap", "bc_reentry": "re-entry",
     "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
-    "bc_latent_prepare": "latent norm + append", "bc_latent_query": "latent query", "bc_latent_rows": "attention", "bc_latent_tiles": "attention",
+    "bc_latent_prepare": "latent norm + append", "bc_latent_query": "latent query", "bc_latent_rows": "attention", "bc_latent_decode": "attention", "bc_latent_heads": "latent query",
+    "bc_latent_gather": "latent keys and values", "bc_latent_spread": "latent keys and values", "bc_latent_gate": "latent values",
     "bc_latent_values": "latent values", "bc_norm_add": "norm", "bc_relu2": "activation", "bc_gated_add": "gated sum", "bc_moe_table_route": "routing",
 }
 
@@ -1097,6 +1098,126 @@ def latent_values(ctx: torch.Tensor, w_uv: torch.Tensor, gate: torch.Tensor, out
         raise KernelError(f"latent_values: ctx {tuple(ctx.shape)}, w_uv {tuple(w_uv.shape)}, out {tuple(out.shape)} do not fit")
     _call(_fn("bc_latent_values_" + _suffix(ctx.dtype)), _ptr(ctx), _ptr(w_uv), _ptr(gate), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_rank),
           _c_int(value_dim), _stream())
+
+
+def latent_decode_accepts(heads: int, kv_rank: int, rot: int, dtype: torch.dtype) -> bool:
+    """Whether the split kernel for single rows takes these sizes (bf16; a latent in multiples of 8 up to 512, a rotated part in
+    multiples of 8 up to 128).  Otherwise latent_rows serves."""
+    return dtype == torch.bfloat16 and bool(_fn("bc_latent_decode_accepts")(_c_int(heads), _c_int(kv_rank), _c_int(rot)))
+
+
+def latent_decode_splits(rows: int, heads: int, reach: int, window: int) -> int:
+    """Splits of the cached positions so that rows * (groups of sixteen heads) * splits blocks come close to two a
+    multiprocessor, never more than a row can see pages (``reach``: a bound on the positions any row reaches)."""
+    tiles = -(-max(reach, 1) // PAGE)
+    if window > 0:
+        tiles = min(tiles, (window + PAGE - 2) // PAGE + 1)
+    blocks = max(1, rows * (-(-heads // 16)))
+    return max(1, min(2 * sm_count() // blocks, tiles, 64))
+
+
+def latent_decode(a: torch.Tensor, c_pages: torch.Tensor, r_pages: Optional[torch.Tensor], page_table: torch.Tensor, row_pos: torch.Tensor,
+                  row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_rank: int, rot: int, window: int, scale: float,
+                  splits: Optional[int] = None, reach: Optional[int] = None) -> None:
+    """What latent_rows computes, for bf16 and few rows: a block takes (row, sixteen heads, split of the cached positions), the
+    heads sharing every read of the cache on mma.sync tiles; several splits are merged in their order by a second kernel.
+    The result does not depend on ``reach``, only the number of splits chosen does."""
+    for t, name in ((a, "a"), (c_pages, "c_pages"), (out, "out")):
+        _need(t, name, torch.bfloat16)
+    _need(page_table, "page_table", torch.int32)
+    rows = a.shape[0]
+    if a.numel() != rows * heads * (kv_rank + rot) or out.numel() != rows * heads * kv_rank or c_pages.shape[-1] != kv_rank:
+        raise KernelError(f"latent_decode: a {tuple(a.shape)}, out {tuple(out.shape)}, pages {tuple(c_pages.shape)} do not fit")
+    if rot > 0:
+        _need(r_pages, "r_pages", torch.bfloat16)
+    if splits is None:
+        splits = latent_decode_splits(rows, heads, page_table.shape[1] * PAGE if reach is None else reach, window)
+    scratch = None
+    if splits > 1:
+        floats = rows * (-(-heads // 16)) * splits * (32 + 16 * (-(-kv_rank // 16) * 16))     # a split leaves 16 maxima, 16 sums, 16 rows
+        scratch, _ = _decode_workspace(a.device, floats, 1)
+    _bounds_paged("latent_decode", rows, row_pos, row_slot, page_table, c_pages.shape[0])
+    _call(_fn("bc_latent_decode_bf16"), _ptr(a), _ptr(c_pages), _ptr(r_pages if rot > 0 else None), _ptr(page_table), _ptr(row_pos), _ptr(row_slot),
+          _ptr(out), _ptr(scratch), _c_int(rows), _c_int(heads), _c_int(kv_rank), _c_int(rot), _c_int(page_table.shape[1]), _c_int(c_pages.shape[0]),
+          _c_int(window), _c_float(scale), _c_int(splits), _stream())
+
+
+def latent_heads(q: torch.Tensor, cos_sin: Optional[torch.Tensor], row_pos: torch.Tensor, out: torch.Tensor, heads: int, dim: int, rot: int) -> None:
+    """out [rows, heads, padded] (bf16) = every head's query as it meets expanded keys: ``dim`` plain values, ``rot`` values rotated
+    by the row's position (pairs (i, i + rot / 2)), zeros up to the padded width.  q float32 [rows, heads * (dim + rot)]."""
+    _need(q, "q", torch.float32)
+    _need(out, "out", torch.bfloat16)
+    rows = q.shape[0]
+    padded = out.numel() // max(rows * heads, 1)
+    if q.shape[1] != heads * (dim + rot) or out.numel() != rows * heads * padded or padded < dim + rot:
+        raise KernelError(f"latent_heads: q {tuple(q.shape)} and out {tuple(out.shape)} do not fit")
+    if rot > 0:
+        _need(cos_sin, "cos_sin", torch.float32)
+        _bounds("latent_heads: row_pos", row_pos, cos_sin.shape[0], rows)
+    _call(_fn("bc_latent_heads_bf16"), _ptr(q), _ptr(cos_sin if rot > 0 else None), _c_int(cos_sin.shape[0] if rot > 0 else 0), _ptr(row_pos), _ptr(out),
+          _c_int(rows), _c_int(heads), _c_int(dim), _c_int(rot), _c_int(padded), _stream())
+
+
+def latent_gather(c_pages: torch.Tensor, r_pages: Optional[torch.Tensor], page_table: torch.Tensor, pg_slot: torch.Tensor, pg_pos: torch.Tensor,
+                  pg_last: torch.Tensor, ctx_c: torch.Tensor, ctx_r: Optional[torch.Tensor], pages: int) -> None:
+    """Copies, for scratch page p, the cache's rows of slot ``pg_slot[p]`` at positions ``pg_pos[p]`` .. + 63 (a multiple of 64)
+    into ctx_c [pages * 64, kv_rank] and ctx_r [pages * 64, rot]; rows past position ``pg_last[p]`` and pages the cache does not
+    hold become zeros."""
+    _need(c_pages, "c_pages", torch.bfloat16)
+    _need(ctx_c, "ctx_c", torch.bfloat16)
+    for t, name in ((page_table, "page_table"), (pg_slot, "pg_slot"), (pg_pos, "pg_pos"), (pg_last, "pg_last")):
+        _need(t, name, torch.int32)
+    R = c_pages.shape[-1]
+    rot = 0 if r_pages is None else r_pages.shape[-1]
+    if ctx_c.numel() < pages * PAGE * R or (rot and (ctx_r is None or ctx_r.numel() < pages * PAGE * rot)) or min(pg_slot.numel(), pg_pos.numel(),
+                                                                                                                 pg_last.numel()) < pages:
+        raise KernelError("latent_gather: the outputs or the pages' lists are shorter than the pages")
+    _bounds("latent_gather: pg_slot", pg_slot, page_table.shape[0], pages, lowest=-1)
+    _call(_fn("bc_latent_gather_bf16"), _ptr(c_pages), _ptr(r_pages), _ptr(page_table), _ptr(pg_slot), _ptr(pg_pos), _ptr(pg_last), _ptr(ctx_c),
+          _ptr(ctx_r if rot else None), _c_int(pages), _c_int(R), _c_int(rot), _c_int(page_table.shape[1]), _c_int(c_pages.shape[0]), _stream())
+
+
+def latent_spread(kv: torch.Tensor, ctx_r: Optional[torch.Tensor], keys: torch.Tensor, values: torch.Tensor, heads: int, dim: int, value_dim: int,
+                  rot: int) -> None:
+    """kv [S, heads * dim + heads * value_dim] (every head's plain key part, then every head's values) and the shared rotated part
+    ctx_r [S, rot] -> keys [S / 64, heads, 64, padded] = [key part | rotated part | zeros] and values [S / 64, heads, 64, padded]."""
+    for t, name in ((kv, "kv"), (keys, "keys"), (values, "values")):
+        _need(t, name, torch.bfloat16)
+    S = kv.shape[0]
+    if kv.shape[1] != heads * (dim + value_dim) or S % PAGE or tuple(keys.shape[:3]) != (S // PAGE, heads, PAGE) \
+            or tuple(values.shape[:3]) != (S // PAGE, heads, PAGE) or keys.shape[3] < dim + rot or values.shape[3] < value_dim:
+        raise KernelError(f"latent_spread: kv {tuple(kv.shape)}, keys {tuple(keys.shape)}, values {tuple(values.shape)} do not fit")
+    if rot > 0:
+        _need(ctx_r, "ctx_r", torch.bfloat16)
+    _call(_fn("bc_latent_spread_bf16"), _ptr(kv), _ptr(ctx_r if rot > 0 else None), _ptr(keys), _ptr(values), _c_int(S), _c_int(heads), _c_int(dim),
+          _c_int(value_dim), _c_int(rot), _c_int(keys.shape[3]), _c_int(values.shape[3]), _stream())
+
+
+def latent_gate(att: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, heads: int, value_dim: int) -> None:
+    """out [rows, heads * value_dim] = att [rows, heads, padded][..., :value_dim] * gate [rows, heads] (float32)."""
+    _need(att, "att", torch.bfloat16)
+    _need(gate, "gate", torch.float32)
+    _need(out, "out", torch.bfloat16)
+    rows = out.shape[0]
+    padded = att.numel() // max(rows * heads, 1)
+    if out.shape[1] != heads * value_dim or att.numel() != rows * heads * padded or padded < value_dim or gate.numel() != rows * heads:
+        raise KernelError(f"latent_gate: att {tuple(att.shape)}, gate {tuple(gate.shape)}, out {tuple(out.shape)} do not fit")
+    _call(_fn("bc_latent_gate_bf16"), _ptr(att), _ptr(gate), _ptr(out), _c_int(rows), _c_int(heads), _c_int(value_dim), _c_int(padded), _stream())
+
+
+def latent_expand_widths(heads: int, key_dim: int, value_dim: int, kv_rank: int, rot: int, dtype: torch.dtype):
+    """(padded key width, padded value width) under which the prompt attention kernels take a latent mixer's expanded keys
+    (``key_dim`` = plain + rotated values a head) and values, or None: bf16, latents and rotated parts in multiples of 8.
+    Widths of 64 and 128 (values no wider than keys) run on the tcgen05 kernel; else equal widths in multiples of 16 up to 128
+    on mma.sync tiles."""
+    if dtype != torch.bfloat16 or kv_rank % 8 or rot % 8 or max(key_dim, value_dim) > 128:
+        return None
+    vp = 64 if value_dim <= 64 else 128
+    kp = max(64 if key_dim <= 64 else 128, vp)
+    if attention_prefill_tc_accepts(heads, heads, kp, value_dim=vp):
+        return kp, vp
+    w = -(-max(key_dim, value_dim) // 16) * 16
+    return (w, w) if attention_tiles_accepts(heads, heads, w, w, dtype) else None
 
 
 # ------------------------------------------------------------- norms after a sublayer, relu squared

@@ -8,8 +8,10 @@ normed vector a position, the latent c (``kv_rank`` values), which is all the ca
     score_n(i, j) = (q_n . Wuk_n c_j + rot(qr_n) . r_j) * scale,   softmax over the visible j
     out = Wo [ sigmoid(zg_n) * Wuv_n sum_j p_n(i, j) c_j ]_n
 
-The scores and the sum over positions run over the cache as it is (the key products are moved to the query's side,
-a_n = Wuk_n^T q_n, and Wuv_n comes after the sum), so a position is read once for all heads and never expanded.
+With few rows a sequence (decoding, short portions) the scores and the sum over positions run over the cache as it is: the
+key products are moved to the query's side, a_n = Wuk_n^T q_n, and Wuv_n comes after the sum, so a position is read once
+for all heads and never expanded.  With many rows a sequence (prompts) what the step sees of the cache is expanded once
+into every head's keys and values, and the prompt attention kernels of the other mixers run over those.
 
 Parameters: a sliding ``window`` (0: every earlier position), the score ``scale`` (default (dim + rot_dim)^-1/2), the
 position encoding of the rotated part (a PartSpec-like mapping; {"kind": "none"} with ``rot_dim`` 0), and ``own_kv``:
@@ -28,7 +30,44 @@ from . import products
 from .base import MIXERS, POSITION_ENCODINGS, CacheNeed, Mixer, RunMemory, Runtime, StepContext, TensorSpec
 
 
-force_rows = False      # tests: the one-warp-a-row kernel (the checked twin) for bfloat16 too
+# Tests: "rows" (the one-warp-a-row kernel, the checked twin), "split" (the split kernel for few rows a sequence) or "expand"
+# (keys and values expanded for the prompt attention kernels) wherever the sizes allow it; None: the part chooses.
+force: Optional[str] = None
+# A sequence that brings at most this many rows takes the split kernel row by row; more are worth expanding what they see.
+SHORT_PORTION = 8
+
+
+def seen_pages(ctx: StepContext, window: int, device: torch.device):
+    """The pages of positions that this step's sequences see, as scratch pages in the order of the sequences: (pages, ints) with
+    ints on the device [6, n]: the slot, first position and last live position of every scratch page; then a page table
+    [seqs, widest] over scratch pages flattened, the sequences' scratch slots, and their starts counted from the first page
+    each sees.  Planned once a step and window (the host knows the lengths of a prompt step)."""
+    key = ("latent_pages", int(window))
+    if key in ctx.extras:
+        return ctx.extras[key]
+    first, count, pg = [], [], []
+    for s in range(ctx.seqs):
+        slot, start = ctx.host_seq_slot[s], ctx.host_seq_start[s]
+        new = ctx.host_seq_rows[s + 1] - ctx.host_seq_rows[s]
+        if slot < 0 or new <= 0:
+            first.append(0), count.append(0)
+            continue
+        lo = max(0, start - window + 1) if window > 0 else 0
+        p0, p1 = lo // ops.PAGE, (start + new - 1) // ops.PAGE
+        first.append(p0), count.append(p1 - p0 + 1)
+        pg += [(slot, ops.PAGE * p, start + new - 1) for p in range(p0, p1 + 1)]
+    pages, widest = len(pg), max(count + [1])
+    table, at = [], 0
+    for n in count:
+        table += list(range(at, at + n)) + [-1] * (widest - n)
+        at += n
+    n = max(pages, ctx.seqs * widest, 1)
+    rows = [[g[0] for g in pg], [g[1] for g in pg], [g[2] for g in pg], table,
+            [s if count[s] else -1 for s in range(ctx.seqs)],
+            [ctx.host_seq_start[s] - ops.PAGE * first[s] for s in range(ctx.seqs)]]
+    ints = torch.tensor([r + [0] * (n - len(r)) for r in rows], dtype=torch.int32).to(device, non_blocking=True)
+    ctx.extras[key] = (pages, widest, ints)
+    return ctx.extras[key]
 
 
 @MIXERS.register("latent_attention")
@@ -79,6 +118,18 @@ class LatentAttention(Mixer):
         self.kv_norm = tensors["dkv.norm"].contiguous() if self.own_kv else None
         self.w_uq, self.w_uk, self.w_uv, self.w_o = (tensors[n].contiguous() for n in ("uq", "uk", "uv", "o"))
         self.position.load({}, rt)
+        # For prompts: one matrix [Wuk; Wuv] that expands gathered latents into every head's plain key part and values.
+        self.widths = ops.latent_expand_widths(self.heads, self.head_dim + self.rot_dim, self.value_dim, self.kv_rank, self.rot_dim, rt.dtype)
+        self.w_ukv = torch.cat([self.w_uk, self.w_uv], dim=0).contiguous() if self.widths is not None else None
+
+    def path(self, ctx: StepContext, dtype: torch.dtype) -> str:
+        split = ops.latent_decode_accepts(self.heads, self.kv_rank, self.rot_dim, dtype)
+        expand = self.widths is not None and dtype == torch.bfloat16 and not ctx.decode and len(ctx.host_seq_rows) > ctx.seqs
+        if force == "rows" or (force == "split" and split) or (force == "expand" and expand):
+            return force
+        if split and (ctx.decode or ctx.max_new <= SHORT_PORTION or not expand):
+            return "split"
+        return "expand" if expand else "rows"
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
         rows, dev = x.shape[0], x.device
@@ -96,19 +147,45 @@ class LatentAttention(Mixer):
                            mem.page_table, c_pages, r_pages, cq, gate, self.norm_eps, write_cache=mem.writes and self.own_kv)
         q = torch.empty((rows, H * (D + ROT)), dtype=torch.float32, device=dev)
         products.linear(cq, self.w_uq, q, products.EPI_STORE_F32, "query up product")
-        a = torch.empty((rows, H, R + ROT), dtype=x.dtype, device=dev)
-        ops.latent_query(q, self.w_uk, cos_sin, ctx.row_pos, a, H, D, ROT, R)
-        found = torch.empty((rows, H, R), dtype=x.dtype, device=dev)
-        self.attend(a, found, ctx, c_pages, r_pages, mem.page_table)
         att = torch.empty((rows, H * DV), dtype=x.dtype, device=dev)
-        ops.latent_values(found, self.w_uv, gate, att, H, R, DV)
+        path = self.path(ctx, x.dtype)
+        if path == "expand":
+            self.expanded(q, gate, att, ctx, c_pages, r_pages, mem.page_table, cos_sin)
+        else:
+            # The key products move to the query's side and the value products come after the sum over positions.
+            a = torch.empty((rows, H, R + ROT), dtype=x.dtype, device=dev)
+            ops.latent_query(q, self.w_uk, cos_sin, ctx.row_pos, a, H, D, ROT, R)
+            found = torch.empty((rows, H, R), dtype=x.dtype, device=dev)
+            if path == "split":
+                ops.latent_decode(a, c_pages, r_pages, mem.page_table, ctx.row_pos, ctx.row_slot, found, H, R, ROT, self.window, self.scale,
+                                  reach=ctx.max_total)
+            else:
+                ops.latent_rows(a, c_pages, r_pages, mem.page_table, ctx.row_pos, ctx.row_slot, found, H, R, ROT, self.window, self.scale)
+            ops.latent_values(found, self.w_uv, gate, att, H, R, DV)
         products.linear(att, self.w_o, residual, products.EPI_ADD_F32, "output product")
 
-    def attend(self, a: torch.Tensor, out: torch.Tensor, ctx: StepContext, c_pages: torch.Tensor, r_pages: Optional[torch.Tensor],
-               page_table: torch.Tensor) -> None:
-        H, R, ROT = self.heads, self.kv_rank, self.rot_dim
-        if not force_rows and hasattr(ops, "latent_tiles") and ops.latent_tiles_accepts(H, R, ROT, a.dtype):
-            ops.latent_tiles(a, c_pages, r_pages, page_table, ctx.seq_rows, ctx.seq_slot, ctx.seq_start, out, ctx.seqs, ctx.max_new, H, R, ROT,
-                             self.window, self.scale)
-            return
-        ops.latent_rows(a, c_pages, r_pages, page_table, ctx.row_pos, ctx.row_slot, out, H, R, ROT, self.window, self.scale)
+    def expanded(self, q: torch.Tensor, gate: torch.Tensor, att: torch.Tensor, ctx: StepContext, c_pages: torch.Tensor,
+                 r_pages: Optional[torch.Tensor], page_table: torch.Tensor, cos_sin: Optional[torch.Tensor]) -> None:
+        """Many rows a sequence: what the step sees of the cache is gathered, multiplied by [Wuk; Wuv] once, laid out as pages of
+        every head's keys [Wuk_n c | r] and values, and the prompt attention kernels run over those pages."""
+        rows, dev, dt = q.shape[0], q.device, att.dtype
+        H, D, DV, R, ROT = self.heads, self.head_dim, self.value_dim, self.kv_rank, self.rot_dim
+        KP, VP = self.widths
+        pages, widest, ints = seen_pages(ctx, self.window, dev)
+        qh = torch.empty((rows, H * KP), dtype=dt, device=dev)
+        ops.latent_heads(q, cos_sin, ctx.row_pos, qh, H, D, ROT)
+        found = torch.zeros((rows, H * VP), dtype=dt, device=dev)      # rows of no sequence are left as they are by the kernels
+        if pages:
+            S = pages * ops.PAGE
+            seen_c = torch.empty((S, R), dtype=dt, device=dev)
+            seen_r = torch.empty((S, ROT), dtype=dt, device=dev) if ROT else None
+            ops.latent_gather(c_pages, r_pages, page_table, ints[0], ints[1], ints[2], seen_c, seen_r, pages)
+            kv = torch.empty((S, H * (D + DV)), dtype=dt, device=dev)
+            products.linear(seen_c, self.w_ukv, kv, products.EPI_STORE, "key and value up product")
+            keys = torch.empty((pages, H, ops.PAGE, KP), dtype=dt, device=dev)
+            values = torch.empty((pages, H, ops.PAGE, VP), dtype=dt, device=dev)
+            ops.latent_spread(kv, seen_r, keys, values, H, D, DV, ROT)
+            scratch_table = ints[3][: ctx.seqs * widest].view(ctx.seqs, widest)
+            ops.attention_prefill(qh, H * KP, keys, values, scratch_table, ctx.seq_rows, ints[4], ints[5], found, ctx.seqs, ctx.max_new, H, H, KP,
+                                  window=self.window, scale=self.scale, value_dim=VP)
+        ops.latent_gate(found, gate, att, H, DV)
