@@ -711,6 +711,121 @@ def bench_pozirax(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=
     return _bench_models(configs, costs_of, c["vocab"], out, pk, rng, FP32_TFLOPS, batch, prompt, steps, warmup)
 
 
+# ------------------------------------------------------------------- the fourth architecture
+FUDELORN_SIZES = {
+    # the width, heads and feed-forward of the 8B shape: latents of 512 (queries 1,536), keys of 64 plain and 64 rotated values on
+    # the layers that rotate and 128 plain ones on the windowed layers; 32 experts of 3,072 of which a row uses 4, a shared one of 2,048
+    "wide": dict(width=4096, heads=32, dim=64, rot=64, wdim=128, vdim=128, q_rank=1536, kv_rank=512, window=1024, ff=14336, experts=32, top=4,
+                 expert_ff=3072, shared=2048, vocab=32000),
+    # a 2,048-wide model: latents of 256, values half as wide as keys
+    "mid": dict(width=2048, heads=16, dim=64, rot=32, wdim=128, vdim=64, q_rank=768, kv_rank=256, window=512, ff=8192, experts=16, top=2,
+                expert_ff=3072, shared=2048, vocab=32000),
+}
+
+
+def fudelorn_config(width, heads, dim, rot, wdim, vdim, q_rank, kv_rank, window, ff, experts, top, expert_ff, shared, vocab, layers):
+    """Layers in turn: a windowed mixer without positions and a dense feed-forward, then a rotating mixer over every earlier
+    position with experts named by the token; every second rotating layer reads the first one's cache."""
+    out, owner = [], None
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer = {"heads": heads, "dim": wdim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "mask": {"size": window}, "scale": wdim ** -0.5}
+            out.append({"type": "latent_attention_2", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+            continue
+        mixer = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": (dim + rot) ** -0.5,
+                 "rot": {"base": 500000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+        if owner is not None:
+            mixer["kv_from"] = owner
+        else:
+            owner = i
+        out.append({"type": "latent_attention", "mixer": mixer,
+                    "mlp": {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}})
+    return {"architecture": "Fudelorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out}
+
+
+def fudelorn_costs(c, layers, batch, ctx_len, T) -> dict:
+    """What each kernel class of the Fudelorn model has to move in a decode step (bytes) and to compute in a prompt step of T
+    tokens (operations, or bytes where it only moves data), summed over the model's layers.  A decode step reads a position's
+    latent once for all heads; a prompt step expands what it sees into every head's keys and values."""
+    E, H, DV, QR, R, W, V = c["width"], c["heads"], c["vdim"], c["q_rank"], c["kv_rank"], c["window"], c["vocab"]
+    X, k, f, fs, F, B = c["experts"], c["top"], c["expert_ff"], c["shared"], c["ff"], batch
+    kinds = []                                            # (plain key width, rotated width, down projection rows, window) of every layer
+    for i in range(layers):
+        own = i % 2 == 0 or i == 1
+        rot, d = (0, c["wdim"]) if i % 2 == 0 else (c["rot"], c["dim"])
+        kinds.append((d, rot, QR + H + (R + rot if own else 0), W if i % 2 == 0 else 0))
+    nd, nm = (layers + 1) // 2, layers // 2               # layers with a dense feed-forward, with experts
+    touched = X * (1.0 - (1.0 - k / X) ** B)
+    decode = {cls: 0.0 for cls in ("latent down product", "latent norm + append", "query up product", "latent query", "attention", "latent values")}
+    prefill = {cls: 0.0 for cls in ("latent down product", "latent norm + append", "query up product", "latent query", "latent keys and values",
+                                    "key and value up product", "attention", "latent values")}
+    for d, rot, P, w in kinds:
+        seen = min(ctx_len + 1, w) if w else ctx_len + 1
+        decode["latent down product"] += 2.0 * P * E + B * (2.0 * E + 4.0 * P)
+        decode["latent norm + append"] += B * (4.0 * P + 2.0 * QR + 4.0 * H + 2.0 * (R + rot))
+        decode["query up product"] += 2.0 * H * (d + rot) * QR + B * (2.0 * QR + 4.0 * H * (d + rot))
+        decode["latent query"] += 2.0 * H * d * R + B * (4.0 * H * (d + rot) + 2.0 * H * (R + rot))
+        decode["attention"] += B * (seen * (R + rot) * 2.0 + 2.0 * H * (R + rot) + 2.0 * H * R)
+        decode["latent values"] += 2.0 * H * DV * R + B * (2.0 * H * R + 4.0 * H + 2.0 * H * DV)
+        pairs = sum(min(t + 1, w) if w else t + 1 for t in range(T))
+        pages = -(-T // 64)
+        prefill["latent down product"] += 2.0 * T * P * E
+        prefill["latent norm + append"] += T * (4.0 * P + 2.0 * QR + 4.0 * H + 2.0 * (R + rot))
+        prefill["query up product"] += 2.0 * T * H * (d + rot) * QR
+        prefill["latent query"] += T * H * (d + rot) * 6.0                                   # the heads' queries rotated and rounded
+        prefill["latent keys and values"] += pages * 64 * (4.0 * (R + rot) + 4.0 * H * (d + DV) + 2.0 * H * rot)
+        prefill["key and value up product"] += 2.0 * pages * 64 * H * (d + DV) * R
+        prefill["attention"] += 2.0 * H * (d + rot + DV) * pairs
+        prefill["latent values"] += T * H * DV * 4.0
+    decode.update({
+        "norm": layers * 2 * (B * E * 6.0 + E * 4.0 + B * E * 12.0 + E * 4.0) + B * E * 6.0,
+        "output product": layers * (2.0 * H * DV * E + B * (2.0 * H * DV + 8.0 * E)),
+        "up product": nd * (2.0 * E * F + B * (2.0 * E + 4.0 * F)) + nm * (2.0 * E * fs + B * (2.0 * E + 4.0 * fs)),
+        "activation": nd * B * F * 6.0 + nm * B * (fs + k * f) * 6.0,
+        "down product": nd * (2.0 * E * F + B * (2.0 * F + 8.0 * E)) + nm * (2.0 * E * fs + B * (2.0 * fs + 8.0 * E)),
+        "routing": nm * B * k * 12.0,
+        "expert sort": nm * B * k * 16.0,
+        "expert gather": nm * B * k * E * 4.0,
+        "expert sum": nm * (B * k * E * 4.0 + B * E * 8.0),
+        "expert product": nm * (touched * 2.0 * f * E * 2.0 + B * k * (2.0 * E + 6.0 * f + 4.0 * E)),
+        "gated sum": nm * (B * E * 14.0 + E * 2.0),
+        "head product": 2.0 * V * E + B * (2.0 * E + 4.0 * V),
+    })
+    prefill = {cls: ("bytes" if cls in ("latent norm + append", "latent query", "latent keys and values", "latent values") else "flops", v)
+               for cls, v in prefill.items()}
+    prefill.update({
+        "norm": ("bytes", layers * 2 * T * E * 18.0),
+        "output product": ("flops", layers * 2.0 * T * H * DV * E),
+        "up product": ("flops", 2.0 * T * E * (nd * F + nm * fs)),
+        "activation": ("bytes", T * 6.0 * (nd * F + nm * (fs + k * f))),
+        "down product": ("flops", 2.0 * T * E * (nd * F + nm * fs)),
+        "routing": ("bytes", nm * T * k * 12.0),
+        "expert sort": ("bytes", nm * T * k * 16.0),
+        "expert gather": ("bytes", nm * T * k * E * 4.0),
+        "expert sum": ("bytes", nm * T * (k * E * 4.0 + E * 8.0)),
+        "expert product": ("flops", nm * 2.0 * T * k * 2.0 * f * E),
+        "gated sum": ("bytes", nm * T * E * 14.0),
+    })
+    return {"decode": decode, "prefill": prefill}
+
+
+def bench_fudelorn(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=32, warmup=4) -> dict:
+    """Prompt and decode throughput of a Fudelorn model of ``layers`` layers at sizes that resemble a real model's layers
+    (random weights), beside a Llama model, the closest of the other designs (softmax attention over a paged cache and a
+    dense feed-forward), of the same width, heads, feed-forward width, vocabulary and depth; every kernel class of both
+    against its own bytes or operations."""
+    c = FUDELORN_SIZES[size]
+    configs = {"fudelorn": fudelorn_config(layers=layers, **c),
+               "llama": llama_like(c["width"], c["heads"], max(1, c["heads"] // 4), 128, c["ff"], c["vocab"], layers)}
+    out = {"size": size, "sizes": c, "layers": layers, "batch": batch, "prompt": prompt,
+           "between": "weights of a step exceed the L2", "peaks": pk, "fp32_cuda_core_tflops_nominal": round(FP32_TFLOPS, 1)}
+
+    def costs_of(name, cfg):
+        return fudelorn_costs(c, layers, batch, prompt + 2, prompt) if name == "fudelorn" else class_costs(cfg, layers, batch, batch * (prompt + 2), prompt)
+
+    return _bench_models(configs, costs_of, c["vocab"], out, pk, rng, FP32_TFLOPS, batch, prompt, steps, warmup)
+
+
 def run_ours(args) -> dict:
     import numpy as np
     import torch
@@ -869,9 +984,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the two other shapes")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-class timing of one decode and one prompt step")
-    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny", "fegidra", "pozirax"],
+    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny", "fegidra", "pozirax", "fudelorn"],
                     help="run one of the further workloads alone and print its figures (not the default run's one JSON line)")
-    ap.add_argument("--size", default="wide", choices=sorted(FEGIDRA_SIZES), help="with --point fegidra or pozirax: which sizes")
+    ap.add_argument("--size", default="wide", choices=sorted(FEGIDRA_SIZES), help="with --point fegidra, pozirax or fudelorn: which sizes")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py or pyproject) "
@@ -889,7 +1004,8 @@ def main() -> int:
         one = {"long": lambda: bench_long(peaks(), rng, args.layers), "13b": lambda: bench_13b(peaks(), rng), "3b": lambda: bench_3b(peaks(), rng),
                "tiny": lambda: bench_tiny(rng),
                "fegidra": lambda: bench_fegidra(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup),
-               "pozirax": lambda: bench_pozirax(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup)}[args.point]
+               "pozirax": lambda: bench_pozirax(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup),
+               "fudelorn": lambda: bench_fudelorn(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup)}[args.point]
         print(json.dumps({"point": args.point, **one()}))
         return 0
     print(json.dumps(run_ours(args)))

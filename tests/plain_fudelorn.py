@@ -28,6 +28,10 @@ import math
 import numpy as np
 
 
+def same(a):
+    return a
+
+
 def rms_norm(x, w, eps):
     x = np.asarray(x, dtype=np.float64)
     return x / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps) * np.asarray(w, dtype=np.float64)
@@ -74,19 +78,19 @@ def softmax_rows(s, ok):
     return p / p.sum(axis=-1, keepdims=True)
 
 
-def latent_keys(h, w, m, eps):
+def latent_keys(h, w, m, eps, r=same):
     """What a layer caches: c [T, kv_rank] and the rotated shared key part [T, rot_dim] (or None)."""
     T = h.shape[0]
     R, rot = int(m["kv_rank"]), int(m.get("rot_dim", 0))
-    z = h @ np.asarray(w["dkv"], dtype=np.float64).T
-    c = rms_norm(z[:, :R], w["dkv.norm"], eps)
+    z = r(h @ np.asarray(w["dkv"], dtype=np.float64).T)
+    c = r(rms_norm(z[:, :R], w["dkv.norm"], eps))
     if rot == 0:
         return c, None
     f, mag = stretched_frequencies(int(m["rot"]["dims"]), float(m["rot"]["base"]), m["rot"].get("scaling"))
-    return c, rotate(z[:, R:R + rot], np.arange(T), f, mag)
+    return c, r(rotate(z[:, R:R + rot], np.arange(T), f, mag))
 
 
-def latent_attention(h, w, m, eps, kept=None):
+def latent_attention(h, w, m, eps, kept=None, r=same):
     """The mixer's output [T, E] for one sequence from position 0; ``kept`` = (c, rotated key part) of
     another layer for a mixer that has no down projection of its own.  Also returns what it keeps."""
     h = np.asarray(h, dtype=np.float64)
@@ -95,11 +99,11 @@ def latent_attention(h, w, m, eps, kept=None):
     R, rot = int(m["kv_rank"]), int(m.get("rot_dim", 0))
     window = int(m["mask"]["size"]) if m.get("mask") else 0
     W = {k: np.asarray(v, dtype=np.float64) for k, v in w.items()}
-    cq = rms_norm(h @ W["dq"].T, W["dq.norm"], eps)
-    q = (cq @ W["uq"].T).reshape(T, H, D + rot)
-    c, kr = latent_keys(h, w, m, eps) if kept is None else kept
-    k = (c @ W["uk"].T).reshape(T, H, D)
-    v = (c @ W["uv"].T).reshape(T, H, DV)
+    cq = r(rms_norm(r(h @ W["dq"].T), W["dq.norm"], eps))
+    q = r(cq @ W["uq"].T).reshape(T, H, D + rot)
+    c, kr = latent_keys(h, w, m, eps, r) if kept is None else kept
+    k = r(c @ W["uk"].T).reshape(T, H, D)
+    v = r(c @ W["uv"].T).reshape(T, H, DV)
     gate = 1.0 / (1.0 + np.exp(-(h @ W["g"].T)))           # [T, H]
     ok = visible(T, window)
     out = np.zeros((T, H, DV))
@@ -108,18 +112,18 @@ def latent_attention(h, w, m, eps, kept=None):
     for n in range(H):
         s = q[:, n, :D] @ k[:, n, :].T
         if rot:
-            s = s + rotate(q[:, n, D:], np.arange(T), f, mag) @ kr.T
+            s = s + r(rotate(q[:, n, D:], np.arange(T), f, mag)) @ kr.T
         p = softmax_rows(s * float(m["scale"]), ok)
-        out[:, n, :] = (p @ v[:, n, :]) * gate[:, n:n + 1]
-    return out.reshape(T, H * DV) @ W["o"].T, (c, kr)
+        out[:, n, :] = r(r(p @ v[:, n, :]) * gate[:, n:n + 1])
+    return r(out.reshape(T, H * DV) @ W["o"].T), (c, kr)
 
 
-def relu_squared_mlp(h, up, down):
+def relu_squared_mlp(h, up, down, r=same):
     z = np.maximum(np.asarray(h, dtype=np.float64) @ np.asarray(up, dtype=np.float64).T, 0.0)
-    return (z * z) @ np.asarray(down, dtype=np.float64).T
+    return r(r(z * z) @ np.asarray(down, dtype=np.float64).T)
 
 
-def table_experts(h, tokens, w, mlp):
+def table_experts(h, tokens, w, mlp, r=same):
     """w: the feed-forward's tensors by the names after 'mlp.'."""
     h = np.asarray(h, dtype=np.float64)
     top = int(mlp["router"]["top"])
@@ -127,39 +131,42 @@ def table_experts(h, tokens, w, mlp):
     out = np.zeros((h.shape[0], np.asarray(w["e0.down"]).shape[0]))
     for t, tok in enumerate(tokens):
         for e in table[int(tok)]:
-            out[t] += relu_squared_mlp(h[t:t + 1], w[f"e{int(e)}.up"], w[f"e{int(e)}.down"])[0] / top
+            out[t] += relu_squared_mlp(h[t:t + 1], w[f"e{int(e)}.up"], w[f"e{int(e)}.down"], r)[0] / top
     if mlp.get("shared"):
         g = 1.0 / (1.0 + np.exp(-(h @ np.asarray(w["shared.sg"], dtype=np.float64).T)))      # [T, 1]
-        out += relu_squared_mlp(h, w["shared.up"], w["shared.down"]) * g
-    return out
+        out += relu_squared_mlp(h, w["shared.up"], w["shared.down"], r) * g
+    return r(out)
 
 
 def sub(tensors, prefix):
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(config, tensors, tokens, taps=None):
-    """Scores [T, vocab] of one sequence's tokens from position 0; ``taps`` (a list) receives the stream after every layer."""
+def forward(config, tensors, tokens, taps=None, r=same):
+    """Scores [T, vocab] of one sequence's tokens from position 0; ``taps`` (a list) receives the stream after every layer.
+    ``r`` is applied wherever the design lets a value be kept in 16 bits (the inputs and results of matrix products and the
+    activations between them; never the stream, a norm's sums, scores or softmax weights): with ``to_bf16`` the scores show how far
+    rounding alone moves each row."""
     eps = float(config["norm"]["eps"])
     x = np.asarray(tensors["embed"], dtype=np.float64)[np.asarray(tokens)]
     kept = {}
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
         m = layer["mixer"]
-        h = rms_norm(x, tensors[p + "norm1"], eps)
-        y, kept[i] = latent_attention(h, sub(tensors, p + "mix."), m, eps, kept.get(m.get("kv_from")) if "kv_from" in m else None)
+        h = r(rms_norm(x, tensors[p + "norm1"], eps))
+        y, kept[i] = latent_attention(h, sub(tensors, p + "mix."), m, eps, kept.get(m.get("kv_from")) if "kv_from" in m else None, r)
         x = x + rms_norm(y, tensors[p + "norm1b"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            h = rms_norm(x, tensors[p + "norm2"], eps)
+            h = r(rms_norm(x, tensors[p + "norm2"], eps))
             if mlp["kind"] == "dense":
-                y = relu_squared_mlp(h, tensors[p + "mlp.up"], tensors[p + "mlp.down"])
+                y = relu_squared_mlp(h, tensors[p + "mlp.up"], tensors[p + "mlp.down"], r)
             else:
-                y = table_experts(h, tokens, sub(tensors, p + "mlp."), mlp)
+                y = table_experts(h, tokens, sub(tensors, p + "mlp."), mlp, r)
             x = x + rms_norm(y, tensors[p + "norm2b"], eps)
         if taps is not None:
             taps.append(x.copy())
-    return rms_norm(x, tensors["final.norm"], eps) @ np.asarray(tensors["head"], dtype=np.float64).T
+    return r(rms_norm(x, tensors["final.norm"], eps)) @ np.asarray(tensors["head"], dtype=np.float64).T
 
 
 # ------------------------------------------------------------------------------ small models for the tests
@@ -222,7 +229,7 @@ def to_bf16(a):
     """Rounds float values to the nearest bfloat16 (ties to even), kept as float32."""
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
     u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
-    return u.astype(np.uint32).view(np.float32)
+    return u.astype(np.uint32).view(np.float32).reshape(np.shape(a))
 
 
 def make_weights(config, seed, spread=1.0):
