@@ -27,6 +27,12 @@ __device__ __forceinline__ float4 lat_load4(const bf16* p) {
     return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
 }
 
+__device__ __forceinline__ float2 lat_load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 lat_load2(const bf16* p) {
+    const unsigned raw = *reinterpret_cast<const unsigned*>(p);
+    return make_float2(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u));
+}
+
 // ------------------------------------------------------------------------------------ prepare
 // One block a row.  proj: [rows, P] float; the q part starts at 0 and is QR wide, the c part at kv_at (R wide, then
 // ROT values of r; kv_at < 0: the mixer reads another layer's cache and has no such part), the gate part at g_at (H wide).
@@ -43,9 +49,11 @@ latent_prepare_kernel(const float* proj, int P, int QR, int kv_at, int R, int RO
     const int r = blockIdx.x;
     const float* x = proj + (size_t)r * P;
     float s = 0.0f;
+#pragma unroll 4
     for (int i = threadIdx.x; i < QR; i += blockDim.x) s = fmaf(x[i], x[i], s);
     s = block_sum(s, scratch);
     const float qs = 1.0f / sqrtf(s / (float)QR + eps);
+#pragma unroll 4
     for (int i = threadIdx.x; i < QR; i += blockDim.x) cq[(size_t)r * QR + i] = from_f32<T>(x[i] * qs * q_w[i]);
     for (int i = threadIdx.x; i < H; i += blockDim.x) gate[(size_t)r * H + i] = 1.0f / (1.0f + expf(-x[g_at + i]));
     if (kv_at < 0 || !write) return;
@@ -55,11 +63,13 @@ latent_prepare_kernel(const float* proj, int P, int QR, int kv_at, int R, int RO
     const int page = pi < max_pages ? page_table[(size_t)slot * max_pages + pi] : -1;
     const float* z = x + kv_at;
     float t = 0.0f;
+#pragma unroll 4
     for (int i = threadIdx.x; i < R; i += blockDim.x) t = fmaf(z[i], z[i], t);
     t = block_sum(t, scratch);
     if (page < 0 || page >= n_pages) return;
     const float cs = 1.0f / sqrtf(t / (float)R + eps);
     const size_t at = (size_t)page * BC_PAGE + pos % BC_PAGE;
+#pragma unroll 4
     for (int i = threadIdx.x; i < R; i += blockDim.x) c_pages[at * R + i] = from_f32<T>(z[i] * cs * kv_w[i]);
     if (ROT > 0 && pos < table_positions) {
         const int half = ROT / 2;
@@ -73,17 +83,23 @@ latent_prepare_kernel(const float* proj, int P, int QR, int kv_at, int R, int RO
 }
 
 // -------------------------------------------------------------------------------------- query
-// Block (x, y): rows LQ_ROWS x .. of head y.  q: [rows, H, D + ROT] float; w_uk: [H * D, R]; a: [rows, H, R + ROT].
+// Block (x, y, z): rows LQ_ROWS x .. of head y, columns LQ_COLS z .. of the latent.  q: [rows, H, D + ROT] float; w_uk: [H * D, R];
+// a: [rows, H, R + ROT].  A lane owns two neighbouring columns and a warp every fourth query dimension, so that few rows
+// still spread over heads * R / LQ_COLS blocks and a thread's loads of the matrix are independent; the warps' parts are
+// added through shared memory.  The block of the first columns also rotates the rotated part.
 #define LQ_ROWS 8
+#define LQ_COLS 64
 template <class T>
 __global__ void __launch_bounds__(128)
 latent_query_kernel(const float* q, const T* __restrict__ w_uk, const float* __restrict__ cos_sin, int table_positions, const int* __restrict__ row_pos,
                     T* __restrict__ a, int rows, int H, int D, int ROT, int R) {
-    extern __shared__ float lq_q[];      // [LQ_ROWS][D]
+    extern __shared__ float lq_q[];      // [LQ_ROWS][D], then the warps' parts [4][LQ_ROWS][LQ_COLS]
+    float* part = lq_q + LQ_ROWS * D;
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(q);
-    const int r0 = blockIdx.x * LQ_ROWS, h = blockIdx.y;
+    const int r0 = blockIdx.x * LQ_ROWS, h = blockIdx.y, n0 = blockIdx.z * LQ_COLS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int QW = D + ROT, AW = R + ROT;
     for (int i = threadIdx.x; i < LQ_ROWS * D; i += blockDim.x) {
         const int rr = r0 + i / D;
@@ -91,19 +107,42 @@ latent_query_kernel(const float* q, const T* __restrict__ w_uk, const float* __r
     }
     __syncthreads();
     const T* w = w_uk + (size_t)h * D * R;
-    for (int n = threadIdx.x; n < R; n += blockDim.x) {
-        float acc[LQ_ROWS];
+    const int n = n0 + 2 * lane;
+    const bool pair = R % 2 == 0;        // then every row of the matrix starts at an even element, and n is even
+    float acc[LQ_ROWS][2];
 #pragma unroll
-        for (int i = 0; i < LQ_ROWS; i++) acc[i] = 0.0f;
-        for (int d = 0; d < D; d++) {
-            const float wv = to_f32(w[(size_t)d * R + n]);
+    for (int i = 0; i < LQ_ROWS; i++) acc[i][0] = acc[i][1] = 0.0f;
+    if (n < R) {
+#pragma unroll 4
+        for (int d = warp; d < D; d += 4) {
+            float w0, w1 = 0.0f;
+            if (pair) {
+                const float2 two = lat_load2(w + (size_t)d * R + n);
+                w0 = two.x, w1 = two.y;
+            } else {
+                w0 = to_f32(w[(size_t)d * R + n]);
+                if (n + 1 < R) w1 = to_f32(w[(size_t)d * R + n + 1]);
+            }
 #pragma unroll
-            for (int i = 0; i < LQ_ROWS; i++) acc[i] = fmaf(lq_q[i * D + d], wv, acc[i]);
+            for (int i = 0; i < LQ_ROWS; i++) {
+                const float qv = lq_q[i * D + d];
+                acc[i][0] = fmaf(qv, w0, acc[i][0]);
+                acc[i][1] = fmaf(qv, w1, acc[i][1]);
+            }
         }
-#pragma unroll
-        for (int i = 0; i < LQ_ROWS; i++)
-            if (r0 + i < rows) a[((size_t)(r0 + i) * H + h) * AW + n] = from_f32<T>(acc[i]);
     }
+#pragma unroll
+    for (int i = 0; i < LQ_ROWS; i++) {
+        part[(warp * LQ_ROWS + i) * LQ_COLS + 2 * lane] = acc[i][0];
+        part[(warp * LQ_ROWS + i) * LQ_COLS + 2 * lane + 1] = acc[i][1];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < LQ_ROWS * LQ_COLS; i += blockDim.x) {
+        const int rr = r0 + i / LQ_COLS, c = n0 + i % LQ_COLS;
+        if (rr < rows && c < R)
+            a[((size_t)rr * H + h) * AW + c] = from_f32<T>(part[i] + part[LQ_ROWS * LQ_COLS + i] + part[2 * LQ_ROWS * LQ_COLS + i] + part[3 * LQ_ROWS * LQ_COLS + i]);
+    }
+    if (blockIdx.z != 0) return;
     const int half = ROT / 2;
     for (int i = threadIdx.x; i < LQ_ROWS * half; i += blockDim.x) {
         const int rr = r0 + i / half, p = i % half;
@@ -208,37 +247,81 @@ latent_rows_kernel(const T* a, const T* c_pages, const T* r_pages, const int* __
 }
 
 // ------------------------------------------------------------------------------------- values
-// Block (x, y): rows LV_ROWS x .. of head y; a warp takes every fourth value channel and adds over R with its lanes.
+// Block (x, y, z): rows LV_ROWS x .. of head y, value channels LV_CH z .. ; a warp takes every fourth of those channels and adds
+// over R with its lanes (four values a load where R allows it), so that few rows spread over heads * DV / LV_CH blocks.
 // ctx: [rows, H, R]; w_uv: [H * DV, R]; gate: [rows, H] float; out: [rows, H * DV].
 #define LV_ROWS 8
+#define LV_CH 16
 template <class T>
 __global__ void __launch_bounds__(128)
 latent_values_kernel(const T* ctx, const T* __restrict__ w_uv, const float* gate, T* __restrict__ out, int rows, int H, int R, int DV) {
-    extern __shared__ float lv_c[];      // [LV_ROWS][R]
+    extern __shared__ __align__(16) float lv_c[];      // [LV_ROWS][R]
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(ctx); PDL_FRESH(gate);
-    const int r0 = blockIdx.x * LV_ROWS, h = blockIdx.y;
+    const int r0 = blockIdx.x * LV_ROWS, h = blockIdx.y, v0 = blockIdx.z * LV_CH;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int i = threadIdx.x; i < LV_ROWS * R; i += blockDim.x) {
-        const int rr = r0 + i / R;
-        lv_c[i] = rr < rows ? to_f32(ctx[((size_t)rr * H + h) * R + i % R]) : 0.0f;
+    const bool four = R % 4 == 0;
+    if (four) {
+        // Four values a load, and the loads of a thread independent of one another: with few rows this fill is the kernel's
+        // longest chain of memory round trips otherwise.
+        const int R4 = R / 4;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < LV_ROWS * R4; i += 128) {
+            const int row = i / R4, c = i - row * R4;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (r0 + row < rows) v = lat_load4(ctx + ((size_t)(r0 + row) * H + h) * R + 4 * c);
+            *reinterpret_cast<float4*>(lv_c + row * R + 4 * c) = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < LV_ROWS * R; i += blockDim.x) {
+            const int rr = r0 + i / R;
+            lv_c[i] = rr < rows ? to_f32(ctx[((size_t)rr * H + h) * R + i % R]) : 0.0f;
+        }
     }
     __syncthreads();
-    for (int v = warp; v < DV; v += 4) {
-        const T* w = w_uv + ((size_t)h * DV + v) * R;
-        float acc[LV_ROWS];
+    // A warp's channels are v0 + warp + 4 j; they run side by side so that their loads of the matrix overlap.
+    constexpr int CW = LV_CH / 4;
+    const int v_end = min(v0 + LV_CH, DV);
+    float acc[CW][LV_ROWS];
 #pragma unroll
-        for (int i = 0; i < LV_ROWS; i++) acc[i] = 0.0f;
-        for (int n = lane; n < R; n += 32) {
-            const float wv = to_f32(w[n]);
+    for (int j = 0; j < CW; j++)
 #pragma unroll
-            for (int i = 0; i < LV_ROWS; i++) acc[i] = fmaf(lv_c[i * R + n], wv, acc[i]);
+        for (int i = 0; i < LV_ROWS; i++) acc[j][i] = 0.0f;
+    const T* w = w_uv + (size_t)h * DV * R;
+    if (four) {
+        for (int n = 4 * lane; n < R; n += 128) {
+            float4 wv[CW];
+#pragma unroll
+            for (int j = 0; j < CW; j++) {
+                const int v = v0 + warp + 4 * j;
+                wv[j] = v < v_end ? lat_load4(w + (size_t)v * R + n) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int i = 0; i < LV_ROWS; i++) {
+                const float4 c = *reinterpret_cast<const float4*>(lv_c + i * R + n);
+#pragma unroll
+                for (int j = 0; j < CW; j++) acc[j][i] = fmaf(c.x, wv[j].x, fmaf(c.y, wv[j].y, fmaf(c.z, wv[j].z, fmaf(c.w, wv[j].w, acc[j][i]))));
+            }
         }
+    } else {
+        for (int n = lane; n < R; n += 32) {
+#pragma unroll
+            for (int j = 0; j < CW; j++) {
+                const int v = v0 + warp + 4 * j;
+                const float wv = v < v_end ? to_f32(w[(size_t)v * R + n]) : 0.0f;
+#pragma unroll
+                for (int i = 0; i < LV_ROWS; i++) acc[j][i] = fmaf(lv_c[i * R + n], wv, acc[j][i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+        const int v = v0 + warp + 4 * j;
 #pragma unroll
         for (int i = 0; i < LV_ROWS; i++) {
-            const float sum = warp_sum(acc[i]);
-            if (lane == 0 && r0 + i < rows) out[(size_t)(r0 + i) * H * DV + (size_t)h * DV + v] = from_f32<T>(sum * gate[(size_t)(r0 + i) * H + h]);
+            const float sum = warp_sum(acc[j][i]);
+            if (lane == 0 && v < v_end && r0 + i < rows) out[(size_t)(r0 + i) * H * DV + (size_t)h * DV + v] = from_f32<T>(sum * gate[(size_t)(r0 + i) * H + h]);
         }
     }
 }
@@ -278,9 +361,10 @@ static int query(const float* q, const void* w_uk, const float* cos_sin, int tab
     BC_CHECK_ARG(rows >= 0 && H > 0 && H <= 65535 && D > 0 && R > 0 && ROT >= 0 && ROT % 2 == 0, "latent_query: bad sizes rows=%d H=%d D=%d R=%d rot=%d", rows,
                  H, D, R, ROT);
     BC_CHECK_ARG(ROT == 0 || cos_sin, "latent_query: a rotation needs its table");
-    BC_CHECK_ARG((size_t)LQ_ROWS * D * sizeof(float) <= 48 * 1024, "latent_query: heads of %d are wider than this kernel takes", D);
+    const size_t shared = ((size_t)LQ_ROWS * D + 4 * LQ_ROWS * LQ_COLS) * sizeof(float);
+    BC_CHECK_ARG(shared <= 48 * 1024 && (R + LQ_COLS - 1) / LQ_COLS <= 65535, "latent_query: heads of %d or a latent of %d are wider than this kernel takes", D, R);
     if (rows == 0) return BC_OK;
-    bc_launch(latent_query_kernel<T>, dim3((rows + LQ_ROWS - 1) / LQ_ROWS, H), dim3(128), (size_t)LQ_ROWS * D * sizeof(float), s, q, (const T*)w_uk, cos_sin,
+    bc_launch(latent_query_kernel<T>, dim3((rows + LQ_ROWS - 1) / LQ_ROWS, H, (R + LQ_COLS - 1) / LQ_COLS), dim3(128), shared, s, q, (const T*)w_uk, cos_sin,
               table_positions, row_pos, (T*)a, rows, H, D, ROT, R);
     BC_LAUNCH_STATUS();
 }
@@ -324,7 +408,7 @@ static int values(const void* ctx, const void* w_uv, const float* gate, void* ou
     BC_CHECK_ARG(rows >= 0 && H > 0 && H <= 65535 && R > 0 && DV > 0, "latent_values: bad sizes rows=%d H=%d R=%d DV=%d", rows, H, R, DV);
     BC_CHECK_ARG((size_t)LV_ROWS * R * sizeof(float) <= 48 * 1024, "latent_values: a latent of %d is wider than this kernel takes", R);
     if (rows == 0) return BC_OK;
-    bc_launch(latent_values_kernel<T>, dim3((rows + LV_ROWS - 1) / LV_ROWS, H), dim3(128), (size_t)LV_ROWS * R * sizeof(float), s, (const T*)ctx,
+    bc_launch(latent_values_kernel<T>, dim3((rows + LV_ROWS - 1) / LV_ROWS, H, (DV + LV_CH - 1) / LV_CH), dim3(128), (size_t)LV_ROWS * R * sizeof(float), s, (const T*)ctx,
               (const T*)w_uv, gate, (T*)out, rows, H, R, DV);
     BC_LAUNCH_STATUS();
 }

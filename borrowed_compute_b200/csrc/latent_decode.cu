@@ -251,27 +251,42 @@ latent_merge_kernel(const float* scratch, const int* __restrict__ row_slot, bf16
     const int RP = ld_up16(R);
     bf16* dst = out + ((size_t)r * H + h) * R;
     const float* part = scratch + ((size_t)r * groups + hg) * splits * ld_partial_floats(R);
+    // The splits' maxima once, in shared memory (a split's number is the thread's), then their weights; every thread adds its
+    // columns over the splits in their order, four columns side by side so that the loads of a split overlap (R <= 512: at
+    // most four columns a thread).
+    __shared__ float wz[64], lz[64];
+    const bool live = row_slot[r] >= 0;
+    if (threadIdx.x < 64) wz[threadIdx.x] = live && threadIdx.x < splits ? part[(size_t)threadIdx.x * ld_partial_floats(R) + row] : -INFINITY;
+    else lz[threadIdx.x - 64] = live && threadIdx.x - 64 < splits ? part[(size_t)(threadIdx.x - 64) * ld_partial_floats(R) + LD_HEADS + row] : 0.0f;
+    __syncthreads();
     float top = -INFINITY;
-    if (row_slot[r] >= 0)
-        for (int z = 0; z < splits; z++) top = fmaxf(top, part[(size_t)z * ld_partial_floats(R) + row]);
+    for (int z = 0; z < splits; z++) top = fmaxf(top, wz[z]);
     if (top == -INFINITY) {
         for (int d = threadIdx.x; d < R; d += blockDim.x) dst[d] = __float2bfloat16_rn(0.0f);
         return;
     }
-    float sum = 0.0f;
+    __syncthreads();
+    if (threadIdx.x < 64) wz[threadIdx.x] = fast_exp2(wz[threadIdx.x] - top);
+    __syncthreads();
+    float total = 0.0f;
+    for (int z = 0; z < splits; z++) total += wz[z] * lz[z];
+    const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 2
     for (int z = 0; z < splits; z++) {
-        const float* p = part + (size_t)z * ld_partial_floats(R);
-        sum += fast_exp2(p[row] - top) * p[LD_HEADS + row];
-    }
-    const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-    for (int d = threadIdx.x; d < R; d += blockDim.x) {
-        float acc = 0.0f;
-        for (int z = 0; z < splits; z++) {
-            const float* p = part + (size_t)z * ld_partial_floats(R);
-            const float w = fast_exp2(p[row] - top);
-            if (w > 0.0f) acc = fmaf(w, p[32 + (size_t)row * RP + d], acc);
+        const float w = wz[z];
+        const float* p = part + (size_t)z * ld_partial_floats(R) + 32 + (size_t)row * RP;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int d = threadIdx.x + 128 * k;
+            const float v = (w > 0.0f && d < R) ? p[d] : 0.0f;      // a split that saw nothing may hold anything
+            acc[k] = fmaf(w, v, acc[k]);
         }
-        dst[d] = __float2bfloat16_rn(acc * inv);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int d = threadIdx.x + 128 * k;
+        if (d < R) dst[d] = __float2bfloat16_rn(acc[k] * inv);
     }
 }
 
@@ -316,8 +331,8 @@ static int decode_launch(const void* a, const void* c_pages, const void* r_pages
 extern "C" int bc_latent_decode_bf16(const void* a, const void* c_pages, const void* r_pages, const int* page_table, const int* row_pos, const int* row_slot,
                                      void* out, float* scratch, int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale,
                                      int splits, cudaStream_t s) {
-    BC_CHECK_ARG(rows >= 0 && bc_latent_decode_accepts(H, R, ROT) && window >= 0 && splits >= 1 && splits <= 65535 && H <= 16 * 65535,
-                 "latent_decode: bad sizes rows=%d H=%d R=%d rot=%d splits=%d (latents in multiples of 8 up to 512, rotated parts up to 128)", rows, H, R, ROT,
+    BC_CHECK_ARG(rows >= 0 && bc_latent_decode_accepts(H, R, ROT) && window >= 0 && splits >= 1 && splits <= 64 && H <= 16 * 65535,
+                 "latent_decode: bad sizes rows=%d H=%d R=%d rot=%d splits=%d (latents in multiples of 8 up to 512, rotated parts up to 128, at most 64 splits)", rows, H, R, ROT,
                  splits);
     BC_CHECK_ARG((ROT == 0 || r_pages) && (splits == 1 || scratch), "latent_decode: rotated keys or scratch memory missing");
     if (rows == 0) return BC_OK;

@@ -2,6 +2,8 @@
 // whose activation is the square of relu.
 //
 //   norm_add     x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w          (y float: the sublayer's result)
+//   norm_add_norm   the same, then h[r] = x[r] / sqrt(mean(x[r]^2) + eps2) * w2 in the activation type for the sublayer that
+//                follows, and y[r] = 0 for its result: one kernel between the two sublayers of a block
 //   relu2        out = max(z, 0)^2 in the activation type               (z float: an up product)
 //   gated_add    x[r] += sigmoid(g . h[r]) * y[r]                       (one number a row: a gate on a shared expert)
 //   table_route  choice[r] = table[token[r]], weight = 1 / top         (experts named by the token id, no router)
@@ -47,6 +49,72 @@ extern "C" int bc_norm_add_f32(const float* y, const float* w, float* x, int row
     if (rows == 0) return BC_OK;
     bc_launch(norm_add_kernel, dim3(rows), dim3(pick(E % 4 == 0 ? E / 4 : E)), 0, s, y, w, x, E, eps);
     BC_LAUNCH_STATUS();
+}
+
+// A thread keeps its columns through both norms: it adds into x the columns whose squares it then sums.
+template <class T>
+__global__ void norm_add_norm_kernel(float* y, const float* __restrict__ wb, float* x, const float* __restrict__ w2, T* __restrict__ h, int E, float eps_b,
+                                     float eps_2) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(y); PDL_FRESH(x);
+    float* yr = y + (size_t)blockIdx.x * E;
+    float* xr = x + (size_t)blockIdx.x * E;
+    T* hr = h + (size_t)blockIdx.x * E;
+    float s = 0.0f, t = 0.0f;
+    if (E % 4 == 0) {
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(yr + c);
+            s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        s = block_sum(s, scratch);
+        const float f = 1.0f / sqrtf(s / (float)E + eps_b);
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(yr + c);
+            const float4 g = *reinterpret_cast<const float4*>(wb + c);
+            float4 o = *reinterpret_cast<float4*>(xr + c);
+            o.x += v.x * f * g.x; o.y += v.y * f * g.y; o.z += v.z * f * g.z; o.w += v.w * f * g.w;
+            *reinterpret_cast<float4*>(xr + c) = o;
+            *reinterpret_cast<float4*>(yr + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            t += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+        }
+        t = block_sum(t, scratch);
+        const float f2 = 1.0f / sqrtf(t / (float)E + eps_2);
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            const float4 o = *reinterpret_cast<const float4*>(xr + c);
+            const float4 g = *reinterpret_cast<const float4*>(w2 + c);
+            hr[c] = from_f32<T>(o.x * f2 * g.x); hr[c + 1] = from_f32<T>(o.y * f2 * g.y);
+            hr[c + 2] = from_f32<T>(o.z * f2 * g.z); hr[c + 3] = from_f32<T>(o.w * f2 * g.w);
+        }
+        return;
+    }
+    for (int c = threadIdx.x; c < E; c += blockDim.x) s += yr[c] * yr[c];
+    s = block_sum(s, scratch);
+    const float f = 1.0f / sqrtf(s / (float)E + eps_b);
+    for (int c = threadIdx.x; c < E; c += blockDim.x) {
+        const float o = xr[c] + yr[c] * f * wb[c];
+        xr[c] = o;
+        yr[c] = 0.0f;
+        t += o * o;
+    }
+    t = block_sum(t, scratch);
+    const float f2 = 1.0f / sqrtf(t / (float)E + eps_2);
+    for (int c = threadIdx.x; c < E; c += blockDim.x) hr[c] = from_f32<T>(xr[c] * f2 * w2[c]);
+}
+
+// y: [rows, E] float, left as zeros; wb, w2: [E] float; x: [rows, E] float, changed in place; h: [rows, E] of the activation type.
+template <class T> static int norm_add_norm(float* y, const float* wb, float* x, const float* w2, void* h, int rows, int E, float eps_b, float eps_2, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && E > 0 && eps_b > 0.0f && eps_2 > 0.0f, "norm_add_norm: bad sizes rows=%d E=%d eps=%g, %g", rows, E, (double)eps_b, (double)eps_2);
+    if (rows == 0) return BC_OK;
+    bc_launch(norm_add_norm_kernel<T>, dim3(rows), dim3(pick(E % 4 == 0 ? E / 4 : E)), 0, s, y, wb, x, w2, (T*)h, E, eps_b, eps_2);
+    BC_LAUNCH_STATUS();
+}
+extern "C" int bc_norm_add_norm_f32(float* y, const float* wb, float* x, const float* w2, void* h, int rows, int E, float eps_b, float eps_2, cudaStream_t s) {
+    return norm_add_norm<float>(y, wb, x, w2, h, rows, E, eps_b, eps_2, s);
+}
+extern "C" int bc_norm_add_norm_bf16(float* y, const float* wb, float* x, const float* w2, void* h, int rows, int E, float eps_b, float eps_2, cudaStream_t s) {
+    return norm_add_norm<bf16>(y, wb, x, w2, h, rows, E, eps_b, eps_2, s);
 }
 
 template <class T>

@@ -1106,14 +1106,20 @@ def latent_decode_accepts(heads: int, kv_rank: int, rot: int, dtype: torch.dtype
     return dtype == torch.bfloat16 and bool(_fn("bc_latent_decode_accepts")(_c_int(heads), _c_int(kv_rank), _c_int(rot)))
 
 
-def latent_decode_splits(rows: int, heads: int, reach: int, window: int) -> int:
-    """Splits of the cached positions so that rows * (groups of sixteen heads) * splits blocks come close to two a
-    multiprocessor, never more than a row can see pages (``reach``: a bound on the positions any row reaches)."""
+def latent_decode_splits(rows: int, heads: int, reach: int, window: int, kv_rank: int = 0, rot: int = 0) -> int:
+    """Splits of the cached positions so that rows * (groups of sixteen heads) * splits blocks fill the machine ONCE: as many
+    blocks as are resident together (two stages of a page's rows [c | r] a block, so wide latents leave one block a
+    multiprocessor and a second wave would double the time), never more than a row can see pages (``reach``: a bound on the
+    positions any row reaches)."""
     tiles = -(-max(reach, 1) // PAGE)
     if window > 0:
         tiles = min(tiles, (window + PAGE - 2) // PAGE + 1)
     blocks = max(1, rows * (-(-heads // 16)))
-    return max(1, min(2 * sm_count() // blocks, tiles, 64))
+    resident = 2
+    if kv_rank > 0:
+        shared = (16 + 2 * PAGE) * (-(-(kv_rank + rot) // 16) * 16 + 8) * 2 + 16 * 72 * 2 + 512
+        resident = max(1, min(8, (227 * 1024) // (shared + 1024)))
+    return max(1, min(resident * sm_count() // blocks, tiles, 64))
 
 
 def latent_decode(a: torch.Tensor, c_pages: torch.Tensor, r_pages: Optional[torch.Tensor], page_table: torch.Tensor, row_pos: torch.Tensor,
@@ -1131,7 +1137,7 @@ def latent_decode(a: torch.Tensor, c_pages: torch.Tensor, r_pages: Optional[torc
     if rot > 0:
         _need(r_pages, "r_pages", torch.bfloat16)
     if splits is None:
-        splits = latent_decode_splits(rows, heads, page_table.shape[1] * PAGE if reach is None else reach, window)
+        splits = latent_decode_splits(rows, heads, page_table.shape[1] * PAGE if reach is None else reach, window, kv_rank, rot)
     scratch = None
     if splits > 1:
         floats = rows * (-(-heads // 16)) * splits * (32 + 16 * (-(-kv_rank // 16) * 16))     # a split leaves 16 maxima, 16 sums, 16 rows
@@ -1231,6 +1237,23 @@ def norm_add(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, eps:
     if residual.shape[0] < rows or residual.shape[1] != E or weight.numel() != E:
         raise KernelError(f"norm_add: y {tuple(y.shape)}, residual {tuple(residual.shape)}, weight {weight.numel()} do not fit")
     _call(_fn("bc_norm_add_f32"), _ptr(y), _ptr(weight), _ptr(residual), _c_int(rows), _c_int(E), _c_float(eps), _stream())
+
+
+def norm_add_norm(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, eps: float, next_weight: torch.Tensor, out: torch.Tensor,
+                  next_eps: float) -> None:
+    """norm_add, then out[r] = residual[r] * rsqrt(mean(residual[r]^2) + next_eps) * next_weight in out's type, and y = 0: what lies
+    between the two sublayers of a block that norms before and after each, in one kernel.  y, residual and the weights float32."""
+    _need(y, "y", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(next_weight, "next_weight", torch.float32)
+    _need(residual, "residual", torch.float32)
+    _need(out, "out")
+    rows, E = y.shape
+    if residual.shape[0] < rows or residual.shape[1] != E or weight.numel() != E or next_weight.numel() != E or tuple(out.shape) != (rows, E):
+        raise KernelError(f"norm_add_norm: y {tuple(y.shape)}, residual {tuple(residual.shape)}, out {tuple(out.shape)}, weights {weight.numel()} and "
+                          f"{next_weight.numel()} do not fit")
+    _call(_fn("bc_norm_add_norm_" + _suffix(out.dtype)), _ptr(y), _ptr(weight), _ptr(residual), _ptr(next_weight), _ptr(out), _c_int(rows), _c_int(E),
+          _c_float(eps), _c_float(next_eps), _stream())
 
 
 def relu2(z: torch.Tensor, out: torch.Tensor) -> None:

@@ -110,9 +110,16 @@ class SandwichBlock(Block):
         y = torch.zeros((rows, self.hidden_size), dtype=torch.float32, device=residual.device)
         self.norm1.forward(residual, h)
         self.mixer.forward(h, y, ctx, mem)
-        ops.norm_add(y, self.norm1b.weight, residual, self.norm1b.eps)
-        if self.feed_forward is not None:
-            y.zero_()
-            self.norm2.forward(residual, h)
+        if self.feed_forward is None:
+            ops.norm_add(y, self.norm1b.weight, residual, self.norm1b.eps)
+        else:
+            # Between the sublayers one kernel: the mixer's result normed into the stream, the stream normed for the
+            # feed-forward, and the buffer cleared for its result.
+            if type(self.norm2) is RMSNorm:
+                ops.norm_add_norm(y, self.norm1b.weight, residual, self.norm1b.eps, self.norm2.weight, h, self.norm2.eps)
+            else:
+                ops.norm_add(y, self.norm1b.weight, residual, self.norm1b.eps)
+                y.zero_()
+                self.norm2.forward(residual, h)
             self.feed_forward.forward(h, y, ctx)
             ops.norm_add(y, self.norm2b.weight, residual, self.norm2b.eps)

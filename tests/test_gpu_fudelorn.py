@@ -326,6 +326,27 @@ def test_the_norm_after_a_sublayer_adds_into_the_stream():
         assert np.abs(res.cpu().numpy() - ref).max() <= 1e-5 * (1 + np.abs(ref).max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_between_the_sublayers_one_kernel_norms_twice_and_clears(dtype):
+    """x += N(y) in float, h = N(x) in the compute type for the feed-forward, y = 0: against the two norms one after the other;
+    widths that four divides and others, a row that is all zeros."""
+    from borrowed_compute_b200 import ops
+
+    rng = np.random.default_rng(4)
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    for width, eps, eps2 in ((96, 1e-5, 1e-6), (250, 1e-6, 1e-5), (4096, 1e-5, 1e-5), (7, 1e-5, 1e-5)):
+        y, x = rng.standard_normal((19, width)) * 3, rng.standard_normal((19, width))
+        y[3] = 0.0
+        w, w2 = 1.0 + 0.3 * rng.uniform(-1, 1, width), 1.0 + 0.3 * rng.uniform(-1, 1, width)
+        yd, res = dev(y.astype(np.float32)), dev(x.astype(np.float32))
+        h = torch.full((19, width), 7.0, dtype=td, device=DEV)
+        ops.norm_add_norm(yd, dev(w.astype(np.float32)), res, eps, dev(w2.astype(np.float32)), h, eps2)
+        ref = x.astype(np.float32) + pf.rms_norm(y.astype(np.float32), w.astype(np.float32), eps)
+        assert np.abs(res.cpu().numpy() - ref).max() <= 1e-5 * (1 + np.abs(ref).max())
+        close(h.float().cpu().numpy(), pf.rms_norm(ref, w2.astype(np.float32), eps2), dtype, f"width {width}")
+        assert float(yd.abs().max()) == 0.0
+
+
 def test_a_mixer_that_reads_another_layers_cache():
     """Two layers, the second without a down projection of its own: it reads what the first cached (the latent and the rotated
     key part as rotated there) with its own key and value matrices, queries and head count; prompts and single rows."""
@@ -467,6 +488,26 @@ def test_drawn_configurations(seed):
         for i in range(3):
             mostly_close(np.concatenate(got[i]), refs[i], dtype, f"{json.dumps(cfg)}: sequence {i} in {dtype}",
                          rounding=rounding_alone(cfg, w, seqs[i], refs[i]) if dtype == "bfloat16" else 0.0)
+
+
+def test_sizes_that_are_multiples_of_nothing():
+    """Widths, ranks, head sizes and a vocabulary that neither 8 nor 16 divides (two rotated dimensions, seven heads of four, one
+    head): the products and the attention fall back to their plain kernels, and a window wider than the sequence hides nothing."""
+    stretch = {"factor": 2.0, "original": 8, "fast": 2.0, "slow": 0.5}
+    cfgs = [{"architecture": "Fudelorn", "vocab": 101, "width": 72, "norm": {"eps": 1e-5}, "layers": [
+                {"type": "latent_attention", "mixer": pf._rotated(3, 12, 24, 12, 20, 2, 10000.0), "mlp": pf._moe(3, 2, 20, shared_ff=12)},
+                {"type": "latent_attention_2", "mixer": pf._windowed(7, 4, 4, 20, 12, 3), "mlp": {"kind": "dense", "ff": 100}},
+                {"type": "latent_attention", "mixer": pf._rotated(1, 20, 12, 4, 20, 2, 10000.0, kv_from=0), "mlp": pf._moe(2, 2, 36)}]},
+            {"architecture": "Fudelorn", "vocab": 33, "width": 50, "norm": {"eps": 1e-6}, "layers": [
+                {"type": "latent_attention_2", "mixer": pf._windowed(2, 6, 10, 6, 10, 1000), "mlp": None},
+                {"type": "latent_attention", "mixer": pf._rotated(2, 10, 6, 14, 6, 6, 100.0, stretch), "mlp": {"kind": "dense", "ff": 30}}]}]
+    for k, cfg in enumerate(cfgs):
+        w = pf.make_weights(cfg, 50 + k)
+        toks = tokens_for(5 + k, 150, cfg["vocab"])
+        ref = pf.forward(cfg, w, toks)
+        for dtype in ("float32", "bfloat16"):
+            eng = engine_for(cfg, w, dtype, max_tokens=1024, max_slots=4, max_seq=256)
+            mostly_close(run_cut(eng, toks, [70, 75]), ref, dtype, f"model {k} in {dtype}")
 
 
 def write_folder(tmp_path, cfg, w):
