@@ -780,14 +780,13 @@ def fudelorn_costs(c, layers, batch, ctx_len, T) -> dict:
     decode.update({
         "norm": layers * 2 * (B * E * 6.0 + E * 4.0 + B * E * 12.0 + E * 4.0) + B * E * 6.0,
         "output product": layers * (2.0 * H * DV * E + B * (2.0 * H * DV + 8.0 * E)),
-        "up product": nd * (2.0 * E * F + B * (2.0 * E + 4.0 * F)) + nm * (2.0 * E * fs + B * (2.0 * E + 4.0 * fs)),
-        "activation": nd * B * F * 6.0 + nm * B * (fs + k * f) * 6.0,
+        "up product": nd * (2.0 * E * F + B * (2.0 * E + 2.0 * F)) + nm * (2.0 * E * fs + B * (2.0 * E + 2.0 * fs)),     # relu^2 in its epilogue
         "down product": nd * (2.0 * E * F + B * (2.0 * F + 8.0 * E)) + nm * (2.0 * E * fs + B * (2.0 * fs + 8.0 * E)),
         "routing": nm * B * k * 12.0,
         "expert sort": nm * B * k * 16.0,
         "expert gather": nm * B * k * E * 4.0,
         "expert sum": nm * (B * k * E * 4.0 + B * E * 8.0),
-        "expert product": nm * (touched * 2.0 * f * E * 2.0 + B * k * (2.0 * E + 6.0 * f + 4.0 * E)),
+        "expert product": nm * (touched * 2.0 * f * E * 2.0 + B * k * (2.0 * E + 4.0 * f + 4.0 * E)),
         "gated sum": nm * (B * E * 14.0 + E * 2.0),
         "head product": 2.0 * V * E + B * (2.0 * E + 4.0 * V),
     })
@@ -797,7 +796,6 @@ def fudelorn_costs(c, layers, batch, ctx_len, T) -> dict:
         "norm": ("bytes", layers * 2 * T * E * 18.0),
         "output product": ("flops", layers * 2.0 * T * H * DV * E),
         "up product": ("flops", 2.0 * T * E * (nd * F + nm * fs)),
-        "activation": ("bytes", T * 6.0 * (nd * F + nm * (fs + k * f))),
         "down product": ("flops", 2.0 * T * E * (nd * F + nm * fs)),
         "routing": ("bytes", nm * T * k * 12.0),
         "expert sort": ("bytes", nm * T * k * 16.0),

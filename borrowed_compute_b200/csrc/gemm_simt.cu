@@ -10,7 +10,7 @@
 // (the residual stream); SwiGLU over a weight that stacks gate rows on up rows.
 #include "common.cuh"
 
-enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
+enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_RELU2 = 4 };
 
 #define BM 64
 #define BN 64
@@ -101,6 +101,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ X,
             if (n >= N) continue;
             const size_t o = (size_t)m * N + n;
             if (EPI == EPI_STORE) out_act[o] = from_f32<T>(acc[i][j]);
+            if (EPI == EPI_RELU2) {
+                const float z = fmaxf(acc[i][j], 0.0f);
+                out_act[o] = from_f32<T>(z * z);
+            }
             if (EPI == EPI_STORE_F32) out_f32[o] = acc[i][j];
             if (EPI == EPI_ADD_F32) out_f32[o] += acc[i][j];
             if (EPI == EPI_SWIGLU) {
@@ -115,7 +119,7 @@ template <class T, int EPI>
 static int launch(const void* X, const void* W, void* out, int M, int N, int K, cudaStream_t s) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     const bool vec = K % 4 == 0 && ((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0);
-    T* oa = (EPI == EPI_STORE || EPI == EPI_SWIGLU) ? (T*)out : nullptr;
+    T* oa = (EPI == EPI_STORE || EPI == EPI_SWIGLU || EPI == EPI_RELU2) ? (T*)out : nullptr;
     float* of = (EPI == EPI_STORE_F32 || EPI == EPI_ADD_F32) ? (float*)out : nullptr;
     if (vec)
         bc_launch(gemm_simt_kernel<T, EPI, true>, grid, dim3(256), 0, s, (const T*)X, (const T*)W, oa, of, M, N, K);
@@ -136,6 +140,7 @@ static int dispatch(const void* X, const void* W, void* out, int M, int N, int K
         case EPI_STORE_F32: return launch<T, EPI_STORE_F32>(X, W, out, M, N, K, s);
         case EPI_ADD_F32: return launch<T, EPI_ADD_F32>(X, W, out, M, N, K, s);
         case EPI_SWIGLU: return launch<T, EPI_SWIGLU>(X, W, out, M, N, K, s);
+        case EPI_RELU2: return launch<T, EPI_RELU2>(X, W, out, M, N, K, s);
     }
     bc_set_error("gemm_simt: unknown epilogue %d", epilogue);
     return BC_ERR_ARG;

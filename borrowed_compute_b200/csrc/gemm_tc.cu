@@ -275,14 +275,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (n >= p.N) return;
                 float r[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : __uint_as_float(v[j]);
+                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : epi_plain<EPI>(__uint_as_float(v[j]));
                 const int t_first = t0 + c0;
                 const size_t o = (size_t)t_first * p.N + n;
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     if (t_first + j >= p.T) break;
                     const size_t at = o + (size_t)j * p.N;
-                    if (EPI == EPI_STORE || EPI == EPI_SWIGLU) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
+                    if (EPI == EPI_STORE || EPI == EPI_SWIGLU || EPI == EPI_RELU2) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
                     if (EPI == EPI_STORE_F32) ((float*)p.out)[at] = r[j];
                     // One thread owns each element, so a fire-and-forget reduction gives the same
                     // sum as a load, add and store, without waiting for the load.
@@ -349,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             auto write = [&](int c, float v, float u) {
                 if (n < p.N) {
                     const size_t o = (size_t)(t0 + c) * p.N + n;
-                    if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(v);
+                    if (EPI == EPI_STORE || EPI == EPI_RELU2) ((bf16*)p.out)[o] = __float2bfloat16_rn(epi_plain<EPI>(v));
                     if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = v;
                     if (EPI == EPI_ADD_F32) ((float*)p.out)[o] += v;   // one owner an element: no reduction needed (and measured 0.4 % of a step faster than a fire-and-forget one)
                     if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(v, u));
@@ -590,14 +590,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (out_n >= p.N) return;
                 float r[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : __uint_as_float(v[j]);
+                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : epi_plain<EPI>(__uint_as_float(v[j]));
                 const int t_first = t0 + c0;
                 const size_t o = (size_t)t_first * p.N + out_n;
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     if (t_first + j >= p.T) break;
                     const size_t at = o + (size_t)j * p.N;
-                    if (EPI == EPI_STORE || EPI == EPI_SWIGLU) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
+                    if (EPI == EPI_STORE || EPI == EPI_SWIGLU || EPI == EPI_RELU2) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
                     if (EPI == EPI_STORE_F32) ((float*)p.out)[at] = r[j];
                     // One thread owns each element, so a fire-and-forget reduction gives the same
                     // sum as a load, add and store, without waiting for the load.
@@ -893,7 +893,7 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     BC_CHECK_ARG(T >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
     BC_CHECK_ARG(K % 8 == 0, "gemm_tc: K=%d is not a multiple of 8 (TMA needs 16-byte row strides); use the CUDA-core product", K);
     BC_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
-    BC_CHECK_ARG(epilogue >= 0 && epilogue <= 3, "gemm_tc: unknown epilogue %d", epilogue);
+    BC_CHECK_ARG(epilogue >= 0 && epilogue <= 4, "gemm_tc: unknown epilogue %d", epilogue);
     BC_CHECK_ARG(splits >= 1, "gemm_tc: bad split count %d", splits);
     if (T == 0) return BC_OK;
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
@@ -930,6 +930,7 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
             case EPI_STORE_F32: return launch_pair<EPI_STORE_F32>(mw, mx, p, s);
             case EPI_ADD_F32: return launch_pair<EPI_ADD_F32>(mw, mx, p, s);
             case EPI_SWIGLU: return launch_pair<EPI_SWIGLU>(mw, mx, p, s);
+            case EPI_RELU2: return launch_pair<EPI_RELU2>(mw, mx, p, s);
         }
     }
     switch (epilogue) {
@@ -937,6 +938,7 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
         case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, stack, mw, mx, p, splits, s);
         case EPI_ADD_F32: return launch_bn<EPI_ADD_F32>(bn, stack, mw, mx, p, splits, s);
         case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, false, mw, mx, p, splits, s);
+        case EPI_RELU2: return launch_bn<EPI_RELU2>(bn, stack, mw, mx, p, splits, s);
     }
     return BC_ERR_ARG;
 }
@@ -1070,12 +1072,12 @@ gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 if (n >= p.N) continue;
                 float r[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : __uint_as_float(v[j]);
+                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : epi_plain<EPI>(__uint_as_float(v[j]));
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     if (cc + j >= t_count) break;
                     const size_t at = (size_t)(t0 + cc + j) * p.N + n;
-                    if (EPI == EPI_SWIGLU) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
+                    if (EPI == EPI_SWIGLU || EPI == EPI_RELU2) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
                     else ((float*)p.out)[at] = r[j];
                 }
             }
@@ -1121,7 +1123,7 @@ static int launch_grouped(const CUtensorMap& mw, const CUtensorMap& mx, TcGroupP
 }
 
 // X [rows, K] bf16, sorted by matrix; W [matrices, N, K] bf16 (gated: [matrices, 2 N, K], gate rows then up rows); out
-// [rows, N]: bf16 silu(gate) * up if gated, else float.  table: [0] tiles; then, a tile, matrix, first row, rows (at most
+// [rows, N]: bf16 silu(gate) * up if gated (1), bf16 max(sum, 0)^2 if gated is 2, else float.  table: [0] tiles; then, a tile, matrix, first row, rows (at most
 // tile_rows, one of 16, 32, 64, 128, 256); max_tiles: the most tiles the table can hold.  K a multiple of 8.
 extern "C" int bc_gemm_tc_grouped_bf16(const void* X, const void* W, void* out, const int* table, int rows, int matrices, int N, int K, int gated,
                                        int tile_rows, int max_tiles, cudaStream_t s) {
@@ -1129,10 +1131,11 @@ extern "C" int bc_gemm_tc_grouped_bf16(const void* X, const void* W, void* out, 
     BC_CHECK_ARG(K % 8 == 0, "gemm_tc_grouped: K=%d is not a multiple of 8 (TMA needs 16-byte row strides)", K);
     BC_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc_grouped: operands must be 16-byte aligned");
     BC_CHECK_ARG(max_tiles > 0 && max_tiles <= 65535, "gemm_tc_grouped: %d tiles are too many", max_tiles);
-    BC_CHECK_ARG((long long)matrices * (gated ? 2 : 1) * N < 2147483647ll, "gemm_tc_grouped: too many weight rows");
+    BC_CHECK_ARG(gated >= 0 && gated <= 2, "gemm_tc_grouped: unknown kind of product %d", gated);
+    BC_CHECK_ARG((long long)matrices * (gated == 1 ? 2 : 1) * N < 2147483647ll, "gemm_tc_grouped: too many weight rows");
     if (rows == 0) return BC_OK;
     CUtensorMap mw, mx;
-    const int matrix_rows = (gated ? 2 : 1) * N;
+    const int matrix_rows = (gated == 1 ? 2 : 1) * N;
     int st = weight_map(&mw, W, matrices * matrix_rows, K);
     if (st != BC_OK) return st;
     st = make_map(&mx, X, rows, K, tile_rows);
@@ -1146,7 +1149,9 @@ extern "C" int bc_gemm_tc_grouped_bf16(const void* X, const void* W, void* out, 
     p.stages = 0;
 #define GROUPED(BN)                                                                         \
     case BN:                                                                                \
-        return gated ? launch_grouped<BN, EPI_SWIGLU>(mw, mx, p, max_tiles, s) : launch_grouped<BN, EPI_STORE_F32>(mw, mx, p, max_tiles, s);
+        return gated == 1 ? launch_grouped<BN, EPI_SWIGLU>(mw, mx, p, max_tiles, s)                \
+               : gated == 2 ? launch_grouped<BN, EPI_RELU2>(mw, mx, p, max_tiles, s)              \
+                            : launch_grouped<BN, EPI_STORE_F32>(mw, mx, p, max_tiles, s);
     switch (tile_rows) {
         GROUPED(16) GROUPED(32) GROUPED(64) GROUPED(128) GROUPED(256)
     }

@@ -7,7 +7,16 @@
 
 #include "common.cuh"
 
-enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
+enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_RELU2 = 4 };
+// What an epilogue without a second operand does to a full sum before it is stored: EPI_RELU2 squares what is above zero (in
+// float; the store rounds once), the others leave it.
+template <int EPI> __device__ __forceinline__ float epi_plain(float v) {
+    if (EPI == EPI_RELU2) {
+        v = fmaxf(v, 0.0f);
+        return v * v;
+    }
+    return v;
+}
 
 #define TC_BM 128          // weight rows a tile (MMA M)
 #define TC_BK 64           // k a stage: 64 bf16 = one 128-byte swizzle row

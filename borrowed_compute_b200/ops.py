@@ -17,7 +17,7 @@ from .csrc import build as _build
 
 PAGE = 64  # tokens per cache page; checked against the library at load
 
-EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
+EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU, EPI_RELU2 = 0, 1, 2, 3, 4
 
 _c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
@@ -274,7 +274,8 @@ def random_normal(out: torch.Tensor, key: int, std: float) -> None:
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
     """out = x @ w.T on the CUDA cores with float accumulation in ascending k.
     EPI_STORE: out in x's type; EPI_STORE_F32: float32; EPI_ADD_F32: out += (float32);
-    EPI_SWIGLU: w stacks gate rows on up rows, out[:, j] = silu(g_j) * u_j in x's type."""
+    EPI_SWIGLU: w stacks gate rows on up rows, out[:, j] = silu(g_j) * u_j in x's type;
+    EPI_RELU2: out = max(sum, 0)^2 in x's type, squared in float and rounded once."""
     _need(x, "x")
     _need(w, "w", x.dtype)
     M, K = x.shape
@@ -487,8 +488,10 @@ def self_check(device: torch.device) -> None:
             product(xb, wb, added, EPI_ADD_F32)
             gated = torch.empty((n, rows_w), dtype=torch.bfloat16, device=device)
             product(xb, wb, gated, EPI_SWIGLU)
+            squared = torch.empty((n, 2 * rows_w), dtype=torch.bfloat16, device=device)
+            product(xb, wb, squared, EPI_RELU2)
             checks = {"store": bad(stored, full, rounded), "store_f32": bad(scores, full), "add_f32": bad(added, full + 0.25),
-                      "swiglu": bad(gated, gate / (1.0 + np.exp(-gate)) * up, rounded)}
+                      "swiglu": bad(gated, gate / (1.0 + np.exp(-gate)) * up, rounded), "relu2": bad(squared, np.maximum(full, 0.0) ** 2, rounded)}
             wrong = [k for k, v in checks.items() if v]
             if wrong:
                 raise KernelError(f"self-check: the {name} product with {n} row(s) is wrong for the epilogue(s) {wrong} on a "
@@ -957,13 +960,17 @@ def gemm_tc_grouped_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
     return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
-def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, table: torch.Tensor, gated: bool, tile_rows: int, max_tiles: int) -> None:
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, table: torch.Tensor, gated: bool, tile_rows: int, max_tiles: int,
+                    relu2: bool = False) -> None:
     """Rows of x [rows, K] sorted by the matrix they meet, times that matrix of w [matrices, N, K] (``gated``: [matrices, 2 N, K],
-    gate rows then up rows, and out = silu(gate) * up in bf16; else out float32 [rows, N]), on the tcgen05 tensor cores.  ``table``
+    gate rows then up rows, and out = silu(gate) * up in bf16; ``relu2``: out = max(sum, 0)^2 in bf16; else out float32 [rows, N]),
+    on the tcgen05 tensor cores.  ``table``
     ([0]: tiles; then matrix, first row, rows a tile of at most ``tile_rows``) comes from ``moe_plan`` with the same ``tile_rows``."""
     _need(x, "x", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
-    _need(out, "out", torch.bfloat16 if gated else torch.float32)
+    if gated and relu2:
+        raise KernelError("gemm_tc_grouped: a gated product has its own activation")
+    _need(out, "out", torch.bfloat16 if gated or relu2 else torch.float32)
     _need(table, "table", torch.int32)
     rows, K = x.shape
     matrices, n_w, kw = w.shape
@@ -971,7 +978,7 @@ def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, table: 
     if kw != K or tuple(out.shape) != (rows, N) or tile_rows not in GROUPED_TILE_ROWS or table.numel() < 1 + 3 * max_tiles:
         raise KernelError(f"gemm_tc_grouped: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, tiles of {tile_rows} do not fit")
     _call(_fn("bc_gemm_tc_grouped_bf16"), _ptr(x), _ptr(w), _ptr(out), _ptr(table), _c_int(rows), _c_int(matrices), _c_int(N), _c_int(K),
-          _c_int(1 if gated else 0), _c_int(tile_rows), _c_int(max_tiles), _stream())
+          _c_int(1 if gated else 2 if relu2 else 0), _c_int(tile_rows), _c_int(max_tiles), _stream())
 
 
 def moe_product(gated: bool, x: torch.Tensor, w: torch.Tensor, table: torch.Tensor, perm: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,

@@ -42,8 +42,8 @@ class SwiGLU(FeedForward):
 
 @FEED_FORWARDS.register("plain_mlp")
 class PlainMLP(FeedForward):
-    """down( act(up x) ) without a gate; ``activation``: "relu2", the square of relu.  The up product keeps its float sums, the
-    activation rounds once.  ``up`` and ``down`` are the names the matrices carry after the part's prefix."""
+    """down( act(up x) ) without a gate; ``activation``: "relu2", the square of relu, applied to the up product's float sums in its
+    epilogue and rounded once.  ``up`` and ``down`` are the names the matrices carry after the part's prefix."""
 
     ACTIVATIONS = ("relu2",)
 
@@ -63,10 +63,6 @@ class PlainMLP(FeedForward):
         self.w_up, self.w_down = tensors[self.names[0]].contiguous(), tensors[self.names[1]].contiguous()
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
-        from .. import ops
-
-        z = torch.empty((x.shape[0], self.intermediate_size), dtype=torch.float32, device=x.device)
-        products.linear(x, self.w_up, z, products.EPI_STORE_F32, "up product")
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.relu2(z, act)
+        products.linear(x, self.w_up, act, products.EPI_RELU2, "up product")
         products.linear(act, self.w_down, residual, products.EPI_ADD_F32, "down product")

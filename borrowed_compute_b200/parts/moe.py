@@ -113,13 +113,14 @@ class RoutedExperts(FeedForward):
             xs = torch.empty((pairs, self.hidden_size), dtype=x.dtype, device=dev)
             ops.moe_gather(x, perm, offsets, weight, xs, E, top, weight_on_input=self.on_input)
         if not self.gated:
-            # Experts without a gate: the up product keeps its float sums, the activation rounds once.
-            z = torch.empty((pairs, self.intermediate_size), dtype=torch.float32, device=dev)
+            # Experts without a gate: the activation works on the up product's float sums and rounds once, in the product's
+            # epilogue on the tensor cores.
             if tensor_cores:
-                ops.gemm_tc_grouped(xs, self.w_gate_up, z, table, False, tile_rows, max_tiles)
+                ops.gemm_tc_grouped(xs, self.w_gate_up, act, table, False, tile_rows, max_tiles, relu2=True)
             else:
+                z = torch.empty((pairs, self.intermediate_size), dtype=torch.float32, device=dev)
                 ops.moe_product(False, xs, self.w_gate_up, table, perm, weight, z, top)
-            ops.relu2(z, act)
+                ops.relu2(z, act)
         elif tensor_cores:
             ops.gemm_tc_grouped(xs, self.w_gate_up, act, table, True, tile_rows, max_tiles)
         else:

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..ops import EPI_ADD_F32, EPI_STORE, EPI_STORE_F32, EPI_SWIGLU  # noqa: F401  (re-exported)
+from ..ops import EPI_ADD_F32, EPI_RELU2, EPI_STORE, EPI_STORE_F32, EPI_SWIGLU  # noqa: F401  (re-exported)
 
 force_simt = False
 

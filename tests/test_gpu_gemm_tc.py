@@ -59,6 +59,10 @@ def test_gemm_tc_all_epilogues(T, N, K, splits):
     unsplit = torch.empty_like(out16)
     ops.gemm_tc(x, w, unsplit, ops.EPI_SWIGLU, splits=1)
     assert np.abs(f64(unsplit) - ref).max() <= 2.0 ** -8 * (1 + np.abs(ref).max()), "SwiGLU, one split"
+    squared = np.maximum(full[:, :N], 0.0) ** 2
+    out16.fill_(7.0)
+    ops.gemm_tc(x, wn, out16, ops.EPI_RELU2, splits=splits)
+    assert np.abs(f64(out16) - squared).max() <= 2.0 ** -8 * (1 + np.abs(squared).max()), "the square of relu"
     assert ops.gemm_tc_status() == 0
 
 
@@ -116,6 +120,8 @@ def test_gemm_tc_many_tokens_on_pairs_of_sms_and_on_single_blocks(T, N, K, paire
         ops.gemm_tc(x, wn, acc, ops.EPI_ADD_F32, splits=1)
         act = torch.full((T, N), 7.0, dtype=torch.bfloat16, device="cuda")
         ops.gemm_tc(x, w, act, ops.EPI_SWIGLU, splits=1)
+        sq = torch.full((T, N), 7.0, dtype=torch.bfloat16, device="cuda")
+        ops.gemm_tc(x, wn, sq, ops.EPI_RELU2, splits=1)
     finally:
         ops.set_gemm_tc_pair(True)
         ops.set_gemm_tc_pair_tokens(0)
@@ -126,6 +132,8 @@ def test_gemm_tc_many_tokens_on_pairs_of_sms_and_on_single_blocks(T, N, K, paire
     g, u = full[:, :N], full[:, N:]
     ref = g / (1 + np.exp(-g)) * u
     assert np.abs(f64(act) - ref).max() <= 2.0 ** -8 * (1 + np.abs(ref).max()), "SwiGLU"
+    squared = np.maximum(full[:, :N], 0.0) ** 2
+    assert np.abs(f64(sq) - squared).max() <= 2.0 ** -8 * (1 + np.abs(squared).max()), "the square of relu"
 
 
 def test_gemm_tc_matches_the_cuda_core_twin():

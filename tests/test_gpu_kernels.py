@@ -108,6 +108,9 @@ def test_gemm_simt(dtype, M, N, K):
     ref = g / (1 + np.exp(-g)) * u
     ops.gemm_simt(xd, wd, out, ops.EPI_SWIGLU)
     assert np.abs(f64(out) - ref).max() <= out_tol(dtype, ref)
+    squared = np.maximum(full[:, :N], 0.0) ** 2
+    ops.gemm_simt(xd, wd[:N].contiguous(), out, ops.EPI_RELU2)
+    assert np.abs(f64(out) - squared).max() <= out_tol(dtype, squared)
 
 
 def poison(kp, vp, table, lengths, drop_before=None):
