@@ -118,14 +118,28 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
             __syncthreads();
         }
         // S for the sixteen heads against this warp's sixteen positions of the page.
-        float s[2][4];
-        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
-        for (int kd = 0; kd < KW / 16; kd++) {
+        // Even and odd steps over the position's values add into sets of their own, so that four chains of products run
+        // side by side, not two of twice the length; the sets are added at the end, in an order the sizes fix.
+        float s[2][4], s_odd[2][4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) s[0][e] = s[1][e] = s_odd[0][e] = s_odd[1][e] = 0.0f;
+        auto s_step = [&](int kd, float (&acc)[2][4]) {
             uint32_t af[4], b0, b1, b2, b3;
             ldmatrix_x4(a_base + ((r8 + 8 * (j4 & 1)) * KWS + (kd * 2 + (j4 >> 1)) * 8) * 2, af[0], af[1], af[2], af[3]);
             ldmatrix_x4(t_base + ((16 * warp + (j4 >> 1) * 8 + r8) * KWS + (kd * 2 + (j4 & 1)) * 8) * 2, b0, b1, b2, b3);
-            mma_16816(s[0], af, b0, b1);
-            mma_16816(s[1], af, b2, b3);
+            mma_16816(acc[0], af, b0, b1);
+            mma_16816(acc[1], af, b2, b3);
+        };
+        const int k_steps = KW / 16;
+        for (int kd = 0; kd + 1 < k_steps; kd += 2) {
+            s_step(kd, s);
+            s_step(kd + 1, s_odd);
+        }
+        if (k_steps & 1) s_step(k_steps - 1, s);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            s[0][e] += s_odd[0][e];
+            s[1][e] += s_odd[1][e];
         }
         float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll

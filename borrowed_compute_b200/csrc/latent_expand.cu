@@ -81,6 +81,25 @@ latent_spread_kernel(const bf16* kv, const bf16* ctx_r, bf16* __restrict__ keys,
     const bf16* src = kv + t * ((size_t)H * (D + DV));
     const bf16* rot = ctx_r + t * ROT;
     const bf16 zero = __float2bfloat16_rn(0.0f);
+    if (D % 8 == 0 && DV % 8 == 0 && ROT % 8 == 0 && KP % 8 == 0 && VP % 8 == 0) {
+        // Eight values (16 bytes) a thread: every part starts at a multiple of eight values, in the source and in the pages.
+        const uint4 none = make_uint4(0u, 0u, 0u, 0u);
+        const int KC = KP / 8, VC = VP / 8;
+        for (int i = threadIdx.x; i < hn * KC; i += blockDim.x) {
+            const int h = h0 + i / KC, d = 8 * (i % KC);
+            uint4 v = none;
+            if (d < D) v = *reinterpret_cast<const uint4*>(src + (size_t)h * D + d);
+            else if (d < D + ROT) v = *reinterpret_cast<const uint4*>(rot + (d - D));
+            *reinterpret_cast<uint4*>(keys + ((page * H + h) * BC_PAGE + row) * KP + d) = v;
+        }
+        for (int i = threadIdx.x; i < hn * VC; i += blockDim.x) {
+            const int h = h0 + i / VC, d = 8 * (i % VC);
+            uint4 v = none;
+            if (d < DV) v = *reinterpret_cast<const uint4*>(src + (size_t)H * D + (size_t)h * DV + d);
+            *reinterpret_cast<uint4*>(values + ((page * H + h) * BC_PAGE + row) * VP + d) = v;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < hn * KP; i += blockDim.x) {
         const int h = h0 + i / KP, d = i % KP;
         keys[((page * H + h) * BC_PAGE + row) * KP + d] = d < D ? src[(size_t)h * D + d] : d < D + ROT ? rot[d - D] : zero;
@@ -98,6 +117,23 @@ latent_gate_kernel(const bf16* att, const float* gate, bf16* __restrict__ out, i
     pdl_wait();
     PDL_FRESH(att); PDL_FRESH(gate);
     const size_t r = blockIdx.x;
+    if (DV % 8 == 0 && VP % 8 == 0) {
+        const int C = DV / 8;
+        for (int i = threadIdx.x; i < H * C; i += blockDim.x) {
+            const int h = i / C, d = 8 * (i - h * C);
+            const float g = gate[r * H + h];
+            uint4 v = *reinterpret_cast<const uint4*>(att + (r * H + h) * VP + d);
+            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float lo = __uint_as_float(w[k] << 16) * g, hi = __uint_as_float(w[k] & 0xffff0000u) * g;
+                const __nv_bfloat162 two = __floats2bfloat162_rn(lo, hi);
+                w[k] = *reinterpret_cast<const uint32_t*>(&two);
+            }
+            *reinterpret_cast<uint4*>(out + r * H * DV + (size_t)h * DV + d) = v;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H * DV; i += blockDim.x) {
         const int h = i / DV, d = i - h * DV;
         out[r * H * DV + i] = __float2bfloat16_rn(__bfloat162float(att[(r * H + h) * VP + d]) * gate[r * H + h]);
