@@ -81,12 +81,22 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
         bf16* dst = tiles + (size_t)stage * BC_PAGE * KWS;
         const bf16* cs = c_pages + (size_t)page * BC_PAGE * R;
         const bf16* rs = r_pages + (size_t)page * BC_PAGE * ROT;
-        for (int i = threadIdx.x; i < BC_PAGE * CH; i += LD_THREADS) {
-            const int row = i / CH, c = i - row * CH;
-            bf16* d = dst + (size_t)row * KWS + c * 8;
-            if (c * 8 < R) cp_async16(ad_smem(d), cs + (size_t)row * R + c * 8);
-            else if (c * 8 < W) cp_async16(ad_smem(d), rs + (size_t)row * ROT + (c * 8 - R));
-            else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+        // A lane keeps its columns (sixteen bytes each, neighbours in a row for neighbouring lanes) and a warp every fourth row:
+        // no division in the loop, which one warp a scheduler issues with nothing to hide behind.
+        for (int c = lane; c < CH; c += 32) {
+            const int col = c * 8;
+            bf16* d = dst + col;
+            if (col < R) {
+                const bf16* src = cs + col;
+#pragma unroll 4
+                for (int row = warp; row < BC_PAGE; row += LD_THREADS / 32) cp_async16(ad_smem(d + (size_t)row * KWS), src + (size_t)row * R);
+            } else if (col < W) {
+                const bf16* src = rs + (col - R);
+#pragma unroll 4
+                for (int row = warp; row < BC_PAGE; row += LD_THREADS / 32) cp_async16(ad_smem(d + (size_t)row * KWS), src + (size_t)row * ROT);
+            } else {
+                for (int row = warp; row < BC_PAGE; row += LD_THREADS / 32) *reinterpret_cast<uint4*>(d + (size_t)row * KWS) = make_uint4(0u, 0u, 0u, 0u);
+            }
         }
     };
 
