@@ -8,16 +8,18 @@
 // A block takes (row, sixteen heads, split of the positions).  The sixteen heads are the rows of m16n8k16 tensor-core
 // tiles.  Pages of 64 positions stream through two stages of shared memory by cp.async as rows [c | r | 0 .. 0] of a
 // multiple of sixteen values, padded by eight so that eight rows fall into eight different banks.  Of a page, each of
-// the four warps takes sixteen positions for S (so the page's keys are multiplied once), the running maximum is the
-// block's (through shared memory), P goes to shared memory as bf16, and each warp takes every fourth pair of eight value
-// columns for O (so the accumulators, 16 x R floats, are spread over the warps).  With one split the block divides and
+// the eight warps takes eight positions for S (so the page's keys are multiplied once; eight warps, because one warp a
+// scheduler has nothing to hide its own latencies behind), the running maximum is the block's (through shared memory),
+// P goes to shared memory as bf16, and each warp takes every eighth pair of eight value columns for O (so the
+// accumulators, 16 x R floats, are spread over the warps).  With one split the block divides and
 // writes; with several every block leaves (maximum, sum, O) in scratch memory and a second kernel merges them in the
 // order of the splits.  Nothing of the launch depends on the lengths, which are read on the device, so a captured graph
 // serves every step.  Sums run in an order that the sizes and the number of splits fix.
 #include "common.cuh"
 #include "mma_tiles.cuh"
 
-#define LD_THREADS 128
+#define LD_THREADS 256
+#define LD_WARPS (LD_THREADS / 32)
 #define LD_STAGES 2
 #define LD_HEADS 16
 #define LD_PS 72            // a row of P in shared memory: 64 positions and eight of padding
@@ -26,7 +28,7 @@ __host__ __device__ __forceinline__ int ld_up16(int n) { return (n + 15) & ~15; 
 // Floats one (row, group of heads, split) leaves in scratch memory: 16 maxima, 16 sums, 16 rows of O.
 __host__ __device__ __forceinline__ size_t ld_partial_floats(int R) { return 32 + (size_t)LD_HEADS * ld_up16(R); }
 
-// MAXP: pairs of eight value columns a warp may own (R <= 64 MAXP).
+// MAXP: pairs of eight value columns a warp may own (R <= 128 MAXP).
 template <int MAXP>
 __global__ void __launch_bounds__(LD_THREADS)
 latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, const int* __restrict__ page_table, const int* __restrict__ row_pos,
@@ -38,7 +40,7 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
     bf16* tiles = As + LD_HEADS * KWS;                         // LD_STAGES x [64][KWS]
     bf16* Ps = tiles + (size_t)LD_STAGES * BC_PAGE * KWS;      // [16][LD_PS]
     float* wmax = reinterpret_cast<float*>(Ps + LD_HEADS * LD_PS);   // [4][16]
-    float* lsum = wmax + 4 * LD_HEADS;                         // [4][16]
+    float* lsum = wmax + LD_WARPS * LD_HEADS;                  // [LD_WARPS][16]
 
     pdl_launch_dependents_if_resident();
     pdl_wait();
@@ -128,38 +130,32 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
             __syncthreads();
         }
         // S for the sixteen heads against this warp's sixteen positions of the page.
-        // Even and odd steps over the position's values add into sets of their own, so that four chains of products run
-        // side by side, not two of twice the length; the sets are added at the end, in an order the sizes fix.
-        float s[2][4], s_odd[2][4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) s[0][e] = s[1][e] = s_odd[0][e] = s_odd[1][e] = 0.0f;
-        auto s_step = [&](int kd, float (&acc)[2][4]) {
-            uint32_t af[4], b0, b1, b2, b3;
-            ldmatrix_x4(a_base + ((r8 + 8 * (j4 & 1)) * KWS + (kd * 2 + (j4 >> 1)) * 8) * 2, af[0], af[1], af[2], af[3]);
-            ldmatrix_x4(t_base + ((16 * warp + (j4 >> 1) * 8 + r8) * KWS + (kd * 2 + (j4 & 1)) * 8) * 2, b0, b1, b2, b3);
-            mma_16816(acc[0], af, b0, b1);
-            mma_16816(acc[1], af, b2, b3);
-        };
+        // S for the sixteen heads against this warp's eight positions of the page.  One load brings the eight positions' values
+        // of two steps; the even and the odd steps add into sets of their own (two chains of products side by side), which
+        // are added at the end, in an order the sizes fix.
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s_odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         const int k_steps = KW / 16;
-        for (int kd = 0; kd + 1 < k_steps; kd += 2) {
-            s_step(kd, s);
-            s_step(kd + 1, s_odd);
+        for (int kd = 0; kd < k_steps; kd += 2) {
+            uint32_t af[4], b0, b1, b2, b3;
+            // Past the last step of an odd count the load reads the row's padding and the start of the next row (inside shared
+            // memory); those two registers are not used.
+            ldmatrix_x4(t_base + ((8 * warp + r8) * KWS + (kd * 2 + j4) * 8) * 2, b0, b1, b2, b3);
+            ldmatrix_x4(a_base + ((r8 + 8 * (j4 & 1)) * KWS + (kd * 2 + (j4 >> 1)) * 8) * 2, af[0], af[1], af[2], af[3]);
+            mma_16816(s, af, b0, b1);
+            if (kd + 1 < k_steps) {
+                ldmatrix_x4(a_base + ((r8 + 8 * (j4 & 1)) * KWS + ((kd + 1) * 2 + (j4 >> 1)) * 8) * 2, af[0], af[1], af[2], af[3]);
+                mma_16816(s_odd, af, b2, b3);
+            }
         }
-        if (k_steps & 1) s_step(k_steps - 1, s);
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-            s[0][e] += s_odd[0][e];
-            s[1][e] += s_odd[1][e];
-        }
+        for (int e = 0; e < 4; e++) s[e] += s_odd[e];
         float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nb = 0; nb < 2; nb++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int t = tile * BC_PAGE + 16 * warp + nb * 8 + 2 * tq + (e & 1);
-                s[nb][e] = t >= lo && t <= pos ? s[nb][e] * scale_log2 : -INFINITY;
-                tmax[e >> 1] = fmaxf(tmax[e >> 1], s[nb][e]);
-            }
+        for (int e = 0; e < 4; e++) {
+            const int t = tile * BC_PAGE + 8 * warp + 2 * tq + (e & 1);
+            s[e] = t >= lo && t <= pos ? s[e] * scale_log2 : -INFINITY;
+            tmax[e >> 1] = fmaxf(tmax[e >> 1], s[e]);
+        }
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
@@ -171,7 +167,9 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             const int row = gq + 8 * i;
-            const float tm = fmaxf(fmaxf(wmax[row], wmax[LD_HEADS + row]), fmaxf(wmax[2 * LD_HEADS + row], wmax[3 * LD_HEADS + row]));
+            float tm = wmax[row];
+#pragma unroll
+            for (int w = 1; w < LD_WARPS; w++) tm = fmaxf(tm, wmax[w * LD_HEADS + row]);
             const float mn = fmaxf(m[i], tm);
             corr[i] = mn == -INFINITY ? 1.0f : fast_exp2(m[i] - mn);
             base[i] = mn == -INFINITY ? 0.0f : mn;
@@ -179,15 +177,14 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
         }
         float psum[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int nb = 0; nb < 2; nb++) {
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                s[nb][e] = fast_exp2(s[nb][e] - base[e >> 1]);
-                psum[e >> 1] += s[nb][e];
-            }
-            const int col = 16 * warp + nb * 8 + 2 * tq;
-            *reinterpret_cast<uint32_t*>(Ps + (size_t)gq * LD_PS + col) = pack_bf16(s[nb][0], s[nb][1]);
-            *reinterpret_cast<uint32_t*>(Ps + (size_t)(gq + 8) * LD_PS + col) = pack_bf16(s[nb][2], s[nb][3]);
+        for (int e = 0; e < 4; e++) {
+            s[e] = fast_exp2(s[e] - base[e >> 1]);
+            psum[e >> 1] += s[e];
+        }
+        {
+            const int col = 8 * warp + 2 * tq;
+            *reinterpret_cast<uint32_t*>(Ps + (size_t)gq * LD_PS + col) = pack_bf16(s[0], s[1]);
+            *reinterpret_cast<uint32_t*>(Ps + (size_t)(gq + 8) * LD_PS + col) = pack_bf16(s[2], s[3]);
         }
         l[0] = l[0] * corr[0] + psum[0];
         l[1] = l[1] * corr[1] + psum[1];
@@ -205,7 +202,7 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
             ldmatrix_x4(p_base + ((r8 + 8 * (j4 & 1)) * LD_PS + (kk * 2 + (j4 >> 1)) * 8) * 2, pf[0], pf[1], pf[2], pf[3]);
 #pragma unroll
             for (int jp = 0; jp < MAXP; jp++) {
-                const int pair = warp + 4 * jp;
+                const int pair = warp + LD_WARPS * jp;
                 if (pair < NPAIR) {
                     uint32_t b0, b1, b2, b3;
                     ldmatrix_x4_trans(t_base + ((kk * 16 + (j4 & 1) * 8 + r8) * KWS + (2 * pair + (j4 >> 1)) * 8) * 2, b0, b1, b2, b3);
@@ -228,7 +225,10 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
 #pragma unroll
     for (int i = 0; i < 2; i++) {
         const int row = gq + 8 * i;
-        total[i] = ((lsum[row] + lsum[LD_HEADS + row]) + lsum[2 * LD_HEADS + row]) + lsum[3 * LD_HEADS + row];
+        float t = lsum[row];
+#pragma unroll
+        for (int w = 1; w < LD_WARPS; w++) t += lsum[w * LD_HEADS + row];
+        total[i] = t;
     }
     if (splits == 1) {
 #pragma unroll
@@ -241,7 +241,7 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
             for (int jp = 0; jp < MAXP; jp++)
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
-                    const int d = (warp + 4 * jp) * 16 + j * 8 + 2 * tq;
+                    const int d = (warp + LD_WARPS * jp) * 16 + j * 8 + 2 * tq;
                     if (d < R) *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16(o[jp][j][2 * i] * inv, o[jp][j][2 * i + 1] * inv);
                 }
         }
@@ -259,7 +259,7 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
         for (int jp = 0; jp < MAXP; jp++)
 #pragma unroll
             for (int j = 0; j < 2; j++) {
-                const int d = (warp + 4 * jp) * 16 + j * 8 + 2 * tq;
+                const int d = (warp + LD_WARPS * jp) * 16 + j * 8 + 2 * tq;
                 if (d < RP) *reinterpret_cast<float2*>(part + 32 + (size_t)row * RP + d) = make_float2(o[jp][j][2 * i], o[jp][j][2 * i + 1]);
             }
     }
@@ -320,7 +320,7 @@ extern "C" int bc_latent_decode_accepts(int H, int R, int ROT) {
 
 static size_t ld_smem_bytes(int R, int ROT) {
     const int KWS = ld_up16(R + ROT) + 8;
-    return (size_t)(LD_HEADS + LD_STAGES * BC_PAGE) * KWS * 2 + LD_HEADS * LD_PS * 2 + 8 * LD_HEADS * sizeof(float);
+    return (size_t)(LD_HEADS + LD_STAGES * BC_PAGE) * KWS * 2 + LD_HEADS * LD_PS * 2 + 2 * LD_WARPS * LD_HEADS * sizeof(float);
 }
 
 extern "C" long long bc_latent_decode_scratch_floats(int rows, int H, int R, int splits) {
@@ -360,7 +360,7 @@ extern "C" int bc_latent_decode_bf16(const void* a, const void* c_pages, const v
                  splits);
     BC_CHECK_ARG((ROT == 0 || r_pages) && (splits == 1 || scratch), "latent_decode: rotated keys or scratch memory missing");
     if (rows == 0) return BC_OK;
-    if (R <= 128) return decode_launch<2>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
-    if (R <= 256) return decode_launch<4>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
-    return decode_launch<8>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
+    if (R <= 128) return decode_launch<1>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
+    if (R <= 256) return decode_launch<2>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
+    return decode_launch<4>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
 }
