@@ -58,7 +58,7 @@ class PagedCache:
             self.groups[g].runs.append(i)
         n_pages = max(1, pages_for(max_tokens))
         self.n_pages = n_pages
-        self.slots = SlotTable(n_slots, n_pages, max_seq, [GroupPlan(g.need.window, g.need.chunk) for g in self.groups])
+        self.slots = SlotTable(n_slots, n_pages, max_seq, [GroupPlan(g.need.window, g.need.chunk, g.need.keep_first) for g in self.groups])
         for g in self.groups:
             g.planes = [torch.zeros((len(g.runs), n_pages, heads, PAGE, width), dtype=rt.dtype, device=rt.device)
                         for heads, width in g.need.planes]

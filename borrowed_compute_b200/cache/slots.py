@@ -62,10 +62,12 @@ class PagePool:
 class GroupPlan:
     """What one storage group keeps per sequence: every position (window 0, chunk 0), the
     last ``window`` of them, and/or only the chunk of ``chunk`` positions (counted from
-    position 0) that the oldest row of a step lies in, and what follows."""
+    position 0) that the oldest row of a step lies in, and what follows.  The pages of the
+    first ``keep_first`` positions are kept whatever else is let go."""
 
     window: int = 0
     chunk: int = 0
+    keep_first: int = 0
 
 
 @dataclass
@@ -140,6 +142,10 @@ class SlotTable:
             oldest_seen = max(oldest_seen, max(0, oldest_row) // c * c)     # the first position of that row's chunk
         return oldest_seen // PAGE
 
+    def _kept_pages(self, g: int) -> int:
+        """Pages at a sequence's start that are never let go: those of its first ``keep_first`` positions."""
+        return pages_for(self.groups[g].keep_first)
+
     def reserve(self, slot: int, new_len: int, rows: int = 1) -> None:
         st = self._held(slot)
         if new_len > self.max_seq:
@@ -155,10 +161,11 @@ class SlotTable:
                                  f"{self.pools[g].available} are free")
         for g, pages in enumerate(st.pages):
             first = self._first_needed_page(g, new_len, rows)
-            dropped = [p for p in pages[:first] if p >= 0]
+            kept = self._kept_pages(g)
+            dropped = [p for p in pages[kept:first] if p >= 0]
             if dropped:
                 self.pools[g].give_back(dropped)
-                for i in range(min(first, len(pages))):
+                for i in range(kept, min(first, len(pages))):
                     pages[i] = -1
             more = need - len(pages)
             if more > 0:
@@ -188,7 +195,7 @@ class SlotTable:
 
     def _releasable(self, g: int, pages: List[int], new_len: int, rows: int) -> int:
         first = self._first_needed_page(g, new_len, rows)
-        return sum(1 for p in pages[:first] if p >= 0)
+        return sum(1 for p in pages[self._kept_pages(g):first] if p >= 0)
 
     def commit(self, slot: int, new_len: int) -> None:
         st = self._held(slot)

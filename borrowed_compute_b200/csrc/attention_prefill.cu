@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(AP_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                          const int* __restrict__ page_table, const int* __restrict__ seq_rows, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G, int max_pages, int n_pages, int window,
-                         int chunk, float scale_log2, int sink, float out_scale) {
+                         int chunk, float scale_log2, int sink, const float* sink_values, float out_scale) {
     constexpr int CHUNKS = D / 8, VCHUNKS = DV / 8;
     constexpr int K_BYTES = 64 * D * 2, TILE_BYTES = 64 * (D + DV) * 2;      // a stage: a page of keys, then its values
     constexpr int KD = D / 16;
@@ -227,8 +227,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
         if (!live[i]) continue;
-        // A sink is one more position of score 0 that has no value: it adds 2^(0 - m) to the sum of the weights alone.
-        if (sink && m[i] != -INFINITY) l[i] += fast_exp2(-m[i]);
+        // A sink is one more position that has no value: it adds 2^(its score - m) to the sum of the weights alone.  Its score is 0, or
+        // the head's own number where a table of them is given.
+        if (sink && m[i] != -INFINITY) l[i] += fast_exp2((sink_values ? sink_values[head[i]] * 1.4426950408889634f : 0.0f) - m[i]);
         const float inv = l[i] > 0.0f ? out_scale / l[i] : 0.0f;
         bf16* dst = out + ((size_t)(row0 + tok[i]) * H + head[i]) * DV + 2 * tq;
 #pragma unroll
@@ -240,7 +241,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 template <int D, int DV>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* seq_rows,
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
-                  int window, int chunk, float scale, int sink, float out_scale, cudaStream_t s) {
+                  int window, int chunk, float scale, int sink, const float* sink_values, float out_scale, cudaStream_t s) {
     constexpr int SMEM = AP_STAGES * 64 * (D + DV) * 2;
     static bool configured = false;
     if (!configured) {
@@ -255,7 +256,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     dim3 grid(G, (max_new + tokens_per_tile - 1) / tokens_per_tile, seqs);
     bc_launch(attention_prefill_kernel<D, DV>, grid, dim3(AP_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
               (const bf16*)v_cache, page_table, seq_rows, seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, chunk,
-              scale * 1.4426950408889634f, sink, out_scale);
+              scale * 1.4426950408889634f, sink, sink_values, out_scale);
     BC_LAUNCH_STATUS();
 }
 
@@ -277,7 +278,7 @@ extern "C" int bc_attention_prefill_bf16(const void* q, int q_stride, const void
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0), "attention_prefill: q and out must be 4-byte aligned");
     if (seqs == 0 || max_new == 0) return BC_OK;
 #define AP_CASE(DD) \
-    case DD: return launch<DD, DD>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, 0, scale, 0, 1.0f, s);
+    case DD: return launch<DD, DD>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, 0, scale, 0, nullptr, 1.0f, s);
     switch (D) {
         AP_CASE(16) AP_CASE(32) AP_CASE(48) AP_CASE(64) AP_CASE(80) AP_CASE(96) AP_CASE(112) AP_CASE(128)
     }
@@ -297,14 +298,14 @@ extern "C" int bc_attention_prefill_kv_accepts(int H, int G, int D, int DV) {
 static int prefill_kv(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                             const int* seq_rows, const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new,
                                             int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk, float scale,
-                                            int sink, float out_scale, cudaStream_t s) {
+                                            int sink, const float* sink_values, float out_scale, cudaStream_t s) {
     BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && max_new < 65535, "attention_prefill: bad sizes seqs=%d max_new=%d", seqs, max_new);
     BC_CHECK_ARG(bc_attention_prefill_kv_accepts(H, G, D, DV), "attention_prefill: H=%d G=%d D=%d DV=%d is outside what this kernel takes", H, G, D, DV);
     BC_CHECK_ARG(window >= 0 && chunk >= 0, "attention_prefill: bad window %d or chunk %d", window, chunk);
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0), "attention_prefill: q and out must be 4-byte aligned");
     if (seqs == 0 || max_new == 0) return BC_OK;
 #define AP_KV(DD, VV) \
-    if (D == DD && DV == VV) return launch<DD, VV>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, sink, out_scale, s);
+    if (D == DD && DV == VV) return launch<DD, VV>(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, sink, sink_values, out_scale, s);
     AP_KV(16, 16) AP_KV(32, 32) AP_KV(48, 48) AP_KV(64, 64) AP_KV(80, 80) AP_KV(96, 96) AP_KV(112, 112) AP_KV(128, 128)
     AP_KV(32, 16) AP_KV(32, 64) AP_KV(32, 128) AP_KV(64, 16) AP_KV(64, 32) AP_KV(64, 128) AP_KV(128, 16) AP_KV(128, 32) AP_KV(128, 64)
 #undef AP_KV
@@ -317,14 +318,14 @@ extern "C" int bc_attention_prefill_kv_bf16(const void* q, int q_stride, const v
                                             int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk, float scale,
                                             cudaStream_t s) {
     return prefill_kv(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, D, DV, max_pages, n_pages,
-                      window, chunk, scale, 0, 1.0f, s);
+                      window, chunk, scale, 0, nullptr, 1.0f, s);
 }
 
-// The same with a sink (one more position of score 0 without a value) and a factor on the output.
+// The same with a sink (one more position without a value, of score 0 or of sink_values[head] if that is not null) and a factor on the output.
 extern "C" int bc_attention_prefill_sink_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                               const int* seq_rows, const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new,
                                               int H, int G, int D, int DV, int max_pages, int n_pages, int window, int chunk, float scale,
-                                              int sink, float out_scale, cudaStream_t s) {
+                                              int sink, const float* sink_values, float out_scale, cudaStream_t s) {
     return prefill_kv(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, D, DV, max_pages, n_pages,
-                      window, chunk, scale, sink, out_scale, s);
+                      window, chunk, scale, sink, sink_values, out_scale, s);
 }

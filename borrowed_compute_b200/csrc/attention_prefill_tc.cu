@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(64 + NT * 128, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, const int* __restrict__ seq_rows,
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G,
-                            int max_pages, int n_pages, int window, int chunk, float scale_log2, int sink, float out_scale) {
+                            int max_pages, int n_pages, int window, int chunk, float scale_log2, int sink, const float* sink_values, float out_scale) {
     constexpr int THREADS = 64 + NT * 128;
     constexpr int STAGES = APT_STAGES(D, NT);
     // P in shared memory only (APT_P_TMEM 0): two P tiles a query tile let the softmax of page
@@ -423,8 +423,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         if (ok) {
             tc_fence_after();
-            // A sink is one more position of score 0 that has no value: it adds 2^(0 - m) to the sum of the weights alone.
-            if (sink && m_used != -INFINITY) l += exp2f(-m_used);
+            // A sink is one more position that has no value: it adds 2^(its score - m) to the sum of the weights alone.  Its score is 0,
+            // or the head's own number where a table of them is given.
+            if (sink && live && m_used != -INFINITY) l += exp2f((sink_values ? sink_values[head] * 1.4426950408889634f : 0.0f) - m_used);
             const float inv = l > 0.0f ? out_scale / l : 0.0f;
             bf16* dst = out + ((size_t)(row0 + tok) * H + head) * DV;
 #pragma unroll 1
@@ -472,7 +473,7 @@ static int query_map(CUtensorMap* map, const void* q, int q_stride, int total_ro
 template <int D, int DV, int NT>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* page_table, const int* seq_rows,
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
-                  int window, int chunk, float scale, int sink, float out_scale, cudaStream_t s) {
+                  int window, int chunk, float scale, int sink, const float* sink_values, float out_scale, cudaStream_t s) {
     constexpr int DB = D / 64;
     constexpr int STAGES = APT_STAGES(D, NT), PB = APT_PB(D, NT);
     constexpr int SMEM = DB * NT * APT_ROWS * 128 + NT * PB * APT_ROWS * 128 + STAGES * 2 * DB * BC_PAGE * 128 + 1024;
@@ -489,7 +490,7 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
     const int tokens_per_block = NT * APT_ROWS / (H / G);
     dim3 grid(G, (max_new + tokens_per_block - 1) / tokens_per_block, seqs);
     cudaError_t e = bc_launch(attention_prefill_tc_kernel<D, DV, NT>, grid, dim3(64 + NT * 128), (size_t)SMEM, s, mq, mk, mv, page_table, seq_rows,
-                              seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, chunk, scale * 1.4426950408889634f, sink, out_scale);
+                              seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, chunk, scale * 1.4426950408889634f, sink, sink_values, out_scale);
     if (e != cudaSuccess) {
         bc_set_error("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
         return (int)e;
@@ -526,7 +527,7 @@ extern "C" int bc_attention_prefill_tc_accepts_kv(int H, int G, int D, int DV) {
 // q and the caches 16-byte aligned, q_stride a multiple of 8.
 static int prefill_tc(const void* q, int q_stride, int total_rows, const void* k_cache, const void* v_cache, const int* page_table,
                       const int* seq_rows, const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int D, int DV,
-                      int max_pages, int n_pages, int window, int chunk, float scale, int sink, float out_scale, cudaStream_t s) {
+                      int max_pages, int n_pages, int window, int chunk, float scale, int sink, const float* sink_values, float out_scale, cudaStream_t s) {
     BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && total_rows >= 0, "attention_prefill_tc: bad sizes seqs=%d max_new=%d rows=%d", seqs,
                  max_new, total_rows);
     BC_CHECK_ARG(bc_attention_prefill_tc_accepts_kv(H, G, D, DV), "attention_prefill_tc: H=%d G=%d D=%d DV=%d is outside what this kernel takes "
@@ -548,7 +549,7 @@ static int prefill_tc(const void* q, int q_stride, int total_rows, const void* k
     const long long cache_rows = (long long)n_pages * G * BC_PAGE;
     if ((st = bc_cached_cache_map(&mk, k_cache, cache_rows, D, "attention_prefill_tc")) != BC_OK) return st;
     if ((st = bc_cached_cache_map(&mv, v_cache, cache_rows, DV, "attention_prefill_tc")) != BC_OK) return st;
-#define APT_GO(DD, VV, NN) return launch<DD, VV, NN>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, sink, out_scale, s)
+#define APT_GO(DD, VV, NN) return launch<DD, VV, NN>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, chunk, scale, sink, sink_values, out_scale, s)
     if (D == 64 && nt == 1) APT_GO(64, 64, 1);
     if (D == 64) APT_GO(64, 64, 2);
     if (DV == 64 && nt == 1) APT_GO(128, 64, 1);
@@ -563,16 +564,16 @@ extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int tot
                                             int seqs, int max_new, int H, int G, int D, int DV, int max_pages, int n_pages, int window,
                                             int chunk, float scale, cudaStream_t s) {
     return prefill_tc(q, q_stride, total_rows, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, D, DV, max_pages,
-                      n_pages, window, chunk, scale, 0, 1.0f, s);
+                      n_pages, window, chunk, scale, 0, nullptr, 1.0f, s);
 }
 
-// The same with a sink (one more position of score 0 without a value) and a factor on the output.
+// The same with a sink (one more position without a value, of score 0 or of sink_values[head] if that is not null) and a factor on the output.
 extern "C" int bc_attention_prefill_tc_sink_bf16(const void* q, int q_stride, int total_rows, const void* k_cache, const void* v_cache,
                                                  const int* page_table, const int* seq_rows, const int* seq_slot, const int* seq_start, void* out,
                                                  int seqs, int max_new, int H, int G, int D, int DV, int max_pages, int n_pages, int window,
-                                                 int chunk, float scale, int sink, float out_scale, cudaStream_t s) {
+                                                 int chunk, float scale, int sink, const float* sink_values, float out_scale, cudaStream_t s) {
     return prefill_tc(q, q_stride, total_rows, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, D, DV, max_pages,
-                      n_pages, window, chunk, scale, sink, out_scale, s);
+                      n_pages, window, chunk, scale, sink, sink_values, out_scale, s);
 }
 
 // This unit's status word (0, or where a bounded wait gave up), its wait limit and its word

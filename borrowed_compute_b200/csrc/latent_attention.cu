@@ -175,11 +175,12 @@ template <class T> __device__ __forceinline__ float lat_dot(const T* k, const fl
 
 #define LR_WARPS 4
 // One warp a (row, head): scores lanes-over-positions, values lanes-over-dimensions, a running maximum and sum.
-// a: [rows, H, R + ROT]; out: [rows, H, R].  NJ = the value dimensions a lane keeps (R <= 32 NJ).
+// a: [rows, H, R + ROT]; out: [rows, H, R]; sink: [H] float or null (one more term e^sink of every row's sum).  NJ = the value dimensions a lane keeps (R <= 32 NJ).
 template <class T, int NJ>
 __global__ void __launch_bounds__(LR_WARPS * 32)
 latent_rows_kernel(const T* a, const T* c_pages, const T* r_pages, const int* __restrict__ page_table, const int* __restrict__ row_pos,
-                   const int* __restrict__ row_slot, T* __restrict__ out, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale) {
+                   const int* __restrict__ row_slot, T* __restrict__ out, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale,
+                   const float* __restrict__ sink) {
     __shared__ __align__(16) float qs[LR_WARPS][LAT_MAX_R + LAT_MAX_ROT];
     pdl_launch_dependents_if_resident();
     pdl_wait();
@@ -238,6 +239,8 @@ latent_rows_kernel(const T* a, const T* c_pages, const T* r_pages, const int* __
         }
         m = mn;
     }
+    // A sink is one more term of the row's sum, e^(the head's number - m), with no key and no value.
+    if (sink != nullptr && m != -INFINITY) l += expf(sink[h] - m);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
@@ -379,7 +382,7 @@ extern "C" int bc_latent_query_bf16(const float* q, const void* w_uk, const floa
 
 template <class T>
 static int rows_launch(const void* a, const void* c_pages, const void* r_pages, const int* page_table, const int* row_pos, const int* row_slot, void* out,
-                       int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale, cudaStream_t s) {
+                       int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale, const float* sink, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && H > 0 && R > 0 && R <= LAT_MAX_R && ROT >= 0 && ROT <= LAT_MAX_ROT && window >= 0,
                  "latent_rows: bad sizes rows=%d H=%d R=%d (at most %d) rot=%d (at most %d)", rows, H, R, LAT_MAX_R, ROT, LAT_MAX_ROT);
     BC_CHECK_ARG((H + LR_WARPS - 1) / LR_WARPS <= 65535 && (ROT == 0 || r_pages), "latent_rows: too many heads (%d) or no rotated keys", H);
@@ -387,7 +390,7 @@ static int rows_launch(const void* a, const void* c_pages, const void* r_pages, 
     dim3 grid(rows, (H + LR_WARPS - 1) / LR_WARPS);
 #define LR_GO(NJ)                                                                                                                                   \
     bc_launch(latent_rows_kernel<T, NJ>, grid, dim3(LR_WARPS * 32), 0, s, (const T*)a, (const T*)c_pages, (const T*)r_pages, page_table, row_pos, \
-              row_slot, (T*)out, H, R, ROT, max_pages, n_pages, window, scale)
+              row_slot, (T*)out, H, R, ROT, max_pages, n_pages, window, scale, sink)
     if (R <= 128) LR_GO(4);
     else if (R <= 256) LR_GO(8);
     else LR_GO(16);
@@ -395,12 +398,14 @@ static int rows_launch(const void* a, const void* c_pages, const void* r_pages, 
     BC_LAUNCH_STATUS();
 }
 extern "C" int bc_latent_rows_f32(const void* a, const void* c_pages, const void* r_pages, const int* page_table, const int* row_pos, const int* row_slot,
-                                  void* out, int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale, cudaStream_t s) {
-    return rows_launch<float>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, rows, H, R, ROT, max_pages, n_pages, window, scale, s);
+                                  void* out, int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale, const float* sink,
+                                  cudaStream_t s) {
+    return rows_launch<float>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, rows, H, R, ROT, max_pages, n_pages, window, scale, sink, s);
 }
 extern "C" int bc_latent_rows_bf16(const void* a, const void* c_pages, const void* r_pages, const int* page_table, const int* row_pos, const int* row_slot,
-                                   void* out, int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale, cudaStream_t s) {
-    return rows_launch<bf16>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, rows, H, R, ROT, max_pages, n_pages, window, scale, s);
+                                   void* out, int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale, const float* sink,
+                                   cudaStream_t s) {
+    return rows_launch<bf16>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, rows, H, R, ROT, max_pages, n_pages, window, scale, sink, s);
 }
 
 template <class T>

@@ -33,7 +33,7 @@ template <int MAXP>
 __global__ void __launch_bounds__(LD_THREADS)
 latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, const int* __restrict__ page_table, const int* __restrict__ row_pos,
                      const int* __restrict__ row_slot, bf16* __restrict__ out, float* __restrict__ scratch, int H, int R, int ROT, int max_pages,
-                     int n_pages, int window, float scale_log2, int splits) {
+                     int n_pages, int window, float scale_log2, int splits, const float* __restrict__ sink) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int W = R + ROT, KW = ld_up16(W), KWS = KW + 8, CH = KW / 8, RP = ld_up16(R), NPAIR = RP / 16;
     bf16* As = reinterpret_cast<bf16*>(smem);                 // [16][KWS]
@@ -235,6 +235,8 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
         for (int i = 0; i < 2; i++) {
             const int head = hg * LD_HEADS + gq + 8 * i;
             if (head >= H) continue;
+            // A sink is one more term of the row's sum, e^(the head's number) against the row's maximum, with no key and no value.
+            if (sink != nullptr && m[i] != -INFINITY) total[i] += fast_exp2(sink[head] * 1.4426950408889634f - m[i]);
             const float inv = total[i] > 0.0f ? 1.0f / total[i] : 0.0f;
             bf16* dst = out + ((size_t)r * H + head) * R;
 #pragma unroll
@@ -267,7 +269,8 @@ latent_decode_kernel(const bf16* a, const bf16* c_pages, const bf16* r_pages, co
 
 // One block a (row, head): the splits' partial results in their order.
 __global__ void __launch_bounds__(128)
-latent_merge_kernel(const float* scratch, const int* __restrict__ row_slot, bf16* __restrict__ out, int H, int R, int groups, int splits) {
+latent_merge_kernel(const float* scratch, const int* __restrict__ row_slot, bf16* __restrict__ out, int H, int R, int groups, int splits,
+                    const float* __restrict__ sink) {
     pdl_launch_dependents_if_resident();
     pdl_wait();
     PDL_FRESH(scratch);
@@ -294,6 +297,7 @@ latent_merge_kernel(const float* scratch, const int* __restrict__ row_slot, bf16
     __syncthreads();
     float total = 0.0f;
     for (int z = 0; z < splits; z++) total += wz[z] * lz[z];
+    if (sink != nullptr) total += fast_exp2(sink[h] * 1.4426950408889634f - top);      // the sink's term, once a row
     const float inv = total > 0.0f ? 1.0f / total : 0.0f;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 2
@@ -329,7 +333,8 @@ extern "C" long long bc_latent_decode_scratch_floats(int rows, int H, int R, int
 
 template <int MAXP>
 static int decode_launch(const void* a, const void* c_pages, const void* r_pages, const int* page_table, const int* row_pos, const int* row_slot, void* out,
-                         float* scratch, int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale, int splits, cudaStream_t s) {
+                         float* scratch, int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale, int splits, const float* sink,
+                         cudaStream_t s) {
     const size_t smem = ld_smem_bytes(R, ROT);
     static size_t configured = 0;
     if (smem > configured) {
@@ -343,24 +348,24 @@ static int decode_launch(const void* a, const void* c_pages, const void* r_pages
     const int groups = (H + LD_HEADS - 1) / LD_HEADS;
     cudaError_t e = bc_launch(latent_decode_kernel<MAXP>, dim3(rows, groups, splits), dim3(LD_THREADS), smem, s, (const bf16*)a, (const bf16*)c_pages,
                               (const bf16*)r_pages, page_table, row_pos, row_slot, (bf16*)out, scratch, H, R, ROT, max_pages, n_pages, window,
-                              scale * 1.4426950408889634f, splits);
+                              scale * 1.4426950408889634f, splits, sink);
     if (e != cudaSuccess) {
         bc_set_error("latent_decode: %s", cudaGetErrorString(e));
         return (int)e;
     }
-    if (splits > 1) bc_launch(latent_merge_kernel, dim3(rows, H), dim3(128), 0, s, (const float*)scratch, row_slot, (bf16*)out, H, R, groups, splits);
+    if (splits > 1) bc_launch(latent_merge_kernel, dim3(rows, H), dim3(128), 0, s, (const float*)scratch, row_slot, (bf16*)out, H, R, groups, splits, sink);
     BC_LAUNCH_STATUS();
 }
 
 extern "C" int bc_latent_decode_bf16(const void* a, const void* c_pages, const void* r_pages, const int* page_table, const int* row_pos, const int* row_slot,
                                      void* out, float* scratch, int rows, int H, int R, int ROT, int max_pages, int n_pages, int window, float scale,
-                                     int splits, cudaStream_t s) {
+                                     int splits, const float* sink, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && bc_latent_decode_accepts(H, R, ROT) && window >= 0 && splits >= 1 && splits <= 64 && H <= 16 * 65535,
                  "latent_decode: bad sizes rows=%d H=%d R=%d rot=%d splits=%d (latents in multiples of 8 up to 512, rotated parts up to 128, at most 64 splits)", rows, H, R, ROT,
                  splits);
     BC_CHECK_ARG((ROT == 0 || r_pages) && (splits == 1 || scratch), "latent_decode: rotated keys or scratch memory missing");
     if (rows == 0) return BC_OK;
-    if (R <= 128) return decode_launch<1>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
-    if (R <= 256) return decode_launch<2>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
-    return decode_launch<4>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, s);
+    if (R <= 128) return decode_launch<1>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, sink, s);
+    if (R <= 256) return decode_launch<2>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, sink, s);
+    return decode_launch<4>(a, c_pages, r_pages, page_table, row_pos, row_slot, out, scratch, rows, H, R, ROT, max_pages, n_pages, window, scale, splits, sink, s);
 }

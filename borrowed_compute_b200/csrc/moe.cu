@@ -75,7 +75,7 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ router, flo
 // One warp a row: the `top` largest logits (the lower index wins a tie) and their scores.
 __global__ void __launch_bounds__(128)
 moe_choose_kernel(const float* __restrict__ logits, const int* __restrict__ row_slot, int* __restrict__ choice, float* __restrict__ weight, int rows,
-                  int E, int top, int softmax, int renorm) {
+                  int E, int top, int softmax, int renorm, float factor) {
     extern __shared__ float score_all[];                    // [4][E]
     pdl_launch_dependents_if_resident();
     pdl_wait();
@@ -130,7 +130,8 @@ moe_choose_kernel(const float* __restrict__ logits, const int* __restrict__ row_
     }
     if (lane < top) {
         choice[(size_t)r * top + lane] = mine_e;
-        weight[(size_t)r * top + lane] = renorm ? mine / picked_sum : mine;
+        // The addend keeps the division defined when every chosen score has underflowed to zero.
+        weight[(size_t)r * top + lane] = (renorm ? mine / (picked_sum + 1e-20f) : mine) * factor;
     }
 }
 
@@ -427,25 +428,25 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ choice, 
 // ------------------------------------------------------------------------------------ launchers
 template <class T>
 static int route(const void* h, const float* router, const int* row_slot, float* logits, int* choice, float* weight, int rows, int E, int K, int top,
-                 int softmax, int renorm, cudaStream_t s) {
+                 int softmax, int renorm, float factor, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && E > 0 && K > 0 && top > 0 && top <= E && top <= MOE_MAX_TOP && E <= 2048, "moe_route: bad sizes rows=%d E=%d K=%d top=%d", rows, E, K, top);
     if (rows == 0) return BC_OK;
     const int groups = (E + ROUTE_EXPERTS - 1) / ROUTE_EXPERTS;
     BC_CHECK_ARG(groups <= 65535, "moe_route: too many experts (%d)", E);
     bc_launch(moe_logits_kernel<T>, dim3((rows + ROUTE_ROWS - 1) / ROUTE_ROWS, groups), dim3(32 * ROUTE_EXPERTS), 0, s, (const T*)h, router, logits, rows, E, K);
     bc_launch(moe_choose_kernel, dim3((rows + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), s, (const float*)logits, row_slot, choice, weight, rows,
-              E, top, softmax, renorm);
+              E, top, softmax, renorm, factor);
     BC_LAUNCH_STATUS();
 }
 // h: [rows, K] of the activation type; router: [E, K] float; row_slot: [rows] (negative: a padding row; may be null);
-// logits: [rows, E] float (scratch); choice: [rows, top] int; weight: [rows, top] float.
+// logits: [rows, E] float (scratch); choice: [rows, top] int; weight: [rows, top] float, every weight times `factor`.
 extern "C" int bc_moe_route_f32(const void* h, const float* router, const int* row_slot, float* logits, int* choice, float* weight, int rows, int E,
-                                int K, int top, int softmax, int renorm, cudaStream_t s) {
-    return route<float>(h, router, row_slot, logits, choice, weight, rows, E, K, top, softmax, renorm, s);
+                                int K, int top, int softmax, int renorm, float factor, cudaStream_t s) {
+    return route<float>(h, router, row_slot, logits, choice, weight, rows, E, K, top, softmax, renorm, factor, s);
 }
 extern "C" int bc_moe_route_bf16(const void* h, const float* router, const int* row_slot, float* logits, int* choice, float* weight, int rows, int E,
-                                 int K, int top, int softmax, int renorm, cudaStream_t s) {
-    return route<bf16>(h, router, row_slot, logits, choice, weight, rows, E, K, top, softmax, renorm, s);
+                                 int K, int top, int softmax, int renorm, float factor, cudaStream_t s) {
+    return route<bf16>(h, router, row_slot, logits, choice, weight, rows, E, K, top, softmax, renorm, factor, s);
 }
 
 extern "C" int bc_moe_max_tiles(int pairs, int E, int tile_rows) { return (pairs + tile_rows - 1) / tile_rows + E; }

@@ -5,6 +5,7 @@
 //   norm_add_norm   the same, then h[r] = x[r] / sqrt(mean(x[r]^2) + eps2) * w2 in the activation type for the sublayer that
 //                follows, and y[r] = 0 for its result: one kernel between the two sublayers of a block
 //   relu2        out = max(z, 0)^2 in the activation type               (z float: an up product)
+//   glu_clipped  out = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit), from z = [g | u] float
 //   gated_add    x[r] += sigmoid(g . h[r]) * y[r]                       (one number a row: a gate on a shared expert)
 //   table_route  choice[r] = table[token[r]], weight = 1 / top         (experts named by the token id, no router)
 //
@@ -136,6 +137,35 @@ template <class T> static int relu2(const float* z, void* out, long long n, cuda
 }
 extern "C" int bc_relu2_f32(const float* z, void* out, long long n, cudaStream_t s) { return relu2<float>(z, out, n, s); }
 extern "C" int bc_relu2_bf16(const float* z, void* out, long long n, cudaStream_t s) { return relu2<bf16>(z, out, n, s); }
+
+// z: [rows, 2 F] float, the gate's sums then the up sums of a row; out: [rows, F].
+template <class T>
+__global__ void glu_clipped_kernel(const float* z, T* __restrict__ out, int F, size_t n, float limit, float alpha) {
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(z);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / F;
+        const int j = (int)(i - r * F);
+        const float g = fminf(z[r * 2 * F + j], limit);
+        const float u = fminf(fmaxf(z[r * 2 * F + F + j], -limit), limit);
+        out[i] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+template <class T> static int glu_clipped(const float* z, void* out, int rows, int F, float limit, float alpha, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && F > 0 && limit > 0.0f, "glu_clipped: bad sizes rows=%d F=%d limit=%g", rows, F, (double)limit);
+    const long long n = (long long)rows * F;
+    if (n == 0) return BC_OK;
+    const long long blocks = (n + 255) / 256;
+    bc_launch(glu_clipped_kernel<T>, dim3((unsigned)(blocks < 65535 * 16 ? blocks : 65535 * 16)), dim3(256), 0, s, z, (T*)out, F, (size_t)n, limit, alpha);
+    BC_LAUNCH_STATUS();
+}
+extern "C" int bc_glu_clipped_f32(const float* z, void* out, int rows, int F, float limit, float alpha, cudaStream_t s) {
+    return glu_clipped<float>(z, out, rows, F, limit, alpha, s);
+}
+extern "C" int bc_glu_clipped_bf16(const float* z, void* out, int rows, int F, float limit, float alpha, cudaStream_t s) {
+    return glu_clipped<bf16>(z, out, rows, F, limit, alpha, s);
+}
 
 template <class T>
 __global__ void gated_add_kernel(const T* h, const T* __restrict__ g, const float* y, float* x, int K, int E) {

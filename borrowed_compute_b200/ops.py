@@ -86,6 +86,14 @@ def _need(t: torch.Tensor, name: str, dtype=None) -> None:
         raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
 
 
+def _sink_values(sink: Optional[torch.Tensor], heads: int, who: str) -> None:
+    """A softmax's learned sinks: float32, one number a head (or None)."""
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
+        if sink.numel() != heads:
+            raise KernelError(f"{who}: {sink.numel()} sink values for {heads} heads")
+
+
 def _suffix(dtype: torch.dtype) -> str:
     if dtype == torch.float32:
         return "f32"
@@ -150,7 +158,8 @@ _CLASS_OF = {
     "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
     "bc_latent_prepare": "latent norm + append", "bc_latent_query": "latent query", "bc_latent_rows": "attention", "bc_latent_decode": "attention", "bc_latent_heads": "latent query",
     "bc_latent_gather": "latent keys and values", "bc_latent_spread": "latent keys and values", "bc_latent_gate": "latent values",
-    "bc_latent_values": "latent values", "bc_norm_add": "norm", "bc_relu2": "activation", "bc_gated_add": "gated sum", "bc_moe_table_route": "routing",
+    "bc_latent_values": "latent values", "bc_norm_add": "norm", "bc_relu2": "activation", "bc_glu_clipped": "activation",
+    "bc_talk_prepare": "rotary + append", "bc_talk_rows": "attention", "bc_talk_tiles": "attention", "bc_scale": "softcap", "bc_add_bias": "bias", "bc_gated_add": "gated sum", "bc_moe_table_route": "routing",
 }
 
 
@@ -889,13 +898,81 @@ def gated_norm(y: torch.Tensor, gate: torch.Tensor, gate_at: int, weight: torch.
           _c_float(factor), _stream())
 
 
+# ---------------------------------------------------------------------- attention whose heads talk
+
+TALK_MAX_HEADS, TALK_MAX_DIM = 64, 256
+
+
+def talk_prepare(proj: torch.Tensor, gate_at: int, bias: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor], row_pos: torch.Tensor,
+                 row_slot: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 gate: torch.Tensor, heads: int, kv_heads: int, head_dim: int, rot: int, eps: float, write_cache: bool = True) -> None:
+    """From the fused projection proj [rows, P] float32 = [q | k | .. gate at ``gate_at`` ..]: q and k plus ``bias`` [(heads + kv_heads)
+    head_dim], the first ``rot`` dimensions of every head rotated by the row's position (pairs (i, i + rot / 2)), every head divided by
+    its root mean square; q into ``q_out`` [rows, heads * head_dim], k into ``k_cache`` and the key as projected (with its bias,
+    neither rotated nor normed) into ``v_cache`` [pages, kv_heads, 64, head_dim] at the row's position; gate = sigmoid, float32
+    [rows, heads * head_dim].  Rows whose slot is negative write no cache."""
+    _need(proj, "proj", torch.float32)
+    _need(q_out, "q_out")
+    _need(k_cache, "k_cache", q_out.dtype)
+    _need(v_cache, "v_cache", q_out.dtype)
+    _need(gate, "gate", torch.float32)
+    _need(page_table, "page_table", torch.int32)
+    rows, P = proj.shape
+    if tuple(q_out.shape) != (rows, heads * head_dim) or gate.shape != q_out.shape or tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) \
+            or v_cache.shape != k_cache.shape:
+        raise KernelError(f"talk_prepare: q {tuple(q_out.shape)}, gate {tuple(gate.shape)}, cache {tuple(k_cache.shape)} and {tuple(v_cache.shape)} do not fit")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != (heads + kv_heads) * head_dim:
+            raise KernelError(f"talk_prepare: {bias.numel()} biases for {(heads + kv_heads) * head_dim} values")
+    if rot > 0:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if tuple(cos_sin.shape[1:]) != (rot // 2, 2):
+            raise KernelError(f"talk_prepare: the rotary table is {tuple(cos_sin.shape)}, {rot} dimensions turn")
+    _bounds_paged("talk_prepare", rows, row_pos, row_slot, page_table, k_cache.shape[0])
+    _call(_fn("bc_talk_prepare_" + _suffix(q_out.dtype)), _ptr(proj), _c_int(rows), _c_int(P), _c_int(gate_at), _ptr(bias), _ptr(cos_sin if rot > 0 else None),
+          _c_int(cos_sin.shape[0] if rot > 0 else 0), _ptr(row_pos), _ptr(row_slot), _ptr(page_table), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]),
+          _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(gate), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(rot), _c_float(eps),
+          _c_int(1 if write_cache else 0), _stream())
+
+
+def _talk_check(who: str, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gate: torch.Tensor, temp: torch.Tensor, talk: torch.Tensor,
+                out: torch.Tensor, heads: int, kv_heads: int, head_dim: int) -> None:
+    _need(q, "q")
+    _need(k_cache, "k_cache", q.dtype)
+    _need(v_cache, "v_cache", q.dtype)
+    _need(out, "out", q.dtype)
+    for t, name in ((gate, "gate"), (temp, "temp"), (talk, "talk")):
+        _need(t, name, torch.float32)
+    rows = q.shape[0]
+    if tuple(q.shape) != (rows, heads * head_dim) or out.shape != q.shape or gate.shape != q.shape or temp.numel() != heads \
+            or talk.numel() != heads * heads or tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or v_cache.shape != k_cache.shape:
+        raise KernelError(f"{who}: q {tuple(q.shape)}, gate {tuple(gate.shape)}, temp {temp.numel()}, talk {tuple(talk.shape)}, "
+                          f"cache {tuple(k_cache.shape)} do not fit {heads} heads on {kv_heads} of {head_dim}")
+
+
+def talk_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, row_pos: torch.Tensor, row_slot: torch.Tensor,
+              gate: torch.Tensor, temp: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
+              keep_first: int, scale: float, cap: float) -> None:
+    """Attention whose heads' scores are mixed before the softmax, one block a row: raw score of head m = q_m . k * scale * temp[m],
+    bounded by cap * tanh(. / cap) if ``cap`` > 0; head h's score = sum_m talk[h, m] raw_m; a row at position i sees j <= i with
+    i - j < window or j < keep_first (window 0: all); out = gate * softmax-weighted sum of v.  Rows whose slot is negative give zeros."""
+    _talk_check("talk_rows", q, k_cache, v_cache, gate, temp, talk, out, heads, kv_heads, head_dim)
+    _need(page_table, "page_table", torch.int32)
+    rows = q.shape[0]
+    _bounds_paged("talk_rows", rows, row_pos, row_slot, page_table, k_cache.shape[0])
+    _call(_fn("bc_talk_rows_" + _suffix(q.dtype)), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(row_pos), _ptr(row_slot), _ptr(gate),
+          _ptr(temp), _ptr(talk), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_table.shape[1]),
+          _c_int(k_cache.shape[0]), _c_int(window), _c_int(keep_first), _c_float(scale), _c_float(cap), _stream())
+
+
 # ------------------------------------------------------------------------------ routed experts
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, row_slot: Optional[torch.Tensor], logits: torch.Tensor, choice: torch.Tensor,
-              weight: torch.Tensor, softmax: bool = False, renorm: bool = False) -> None:
+              weight: torch.Tensor, softmax: bool = False, renorm: bool = False, factor: float = 1.0) -> None:
     """choice [rows, top] (int32), weight [rows, top] (float32): every row's ``top`` experts by score, the lower index winning a tie.
     Scores are sigmoid(router @ h) (or a softmax over the experts), computed in float32; weights are the chosen scores, divided by
-    their sum with ``renorm``.  Rows whose slot is negative choose nothing (-1).  ``logits`` [rows, experts] float32 receives router @ h."""
+    their sum with ``renorm``, then times ``factor``.  Rows whose slot is negative choose nothing (-1).  ``logits`` [rows, experts] float32 receives router @ h."""
     _need(h, "h")
     _need(router, "router", torch.float32)
     _need(logits, "logits", torch.float32)
@@ -908,7 +985,7 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, row_slot: Optional[torch.Te
     if row_slot is not None:
         _need(row_slot, "row_slot", torch.int32)
     _call(_fn("bc_moe_route_" + _suffix(h.dtype)), _ptr(h), _ptr(router), _ptr(row_slot), _ptr(logits), _ptr(choice), _ptr(weight), _c_int(rows), _c_int(E),
-          _c_int(K), _c_int(top), _c_int(1 if softmax else 0), _c_int(1 if renorm else 0), _stream())
+          _c_int(K), _c_int(top), _c_int(1 if softmax else 0), _c_int(1 if renorm else 0), _c_float(factor), _stream())
 
 
 def moe_simt_tile_rows() -> int:
@@ -1072,12 +1149,15 @@ LATENT_MAX_RANK, LATENT_MAX_ROT = 512, 128
 
 
 def latent_rows(a: torch.Tensor, c_pages: torch.Tensor, r_pages: Optional[torch.Tensor], page_table: torch.Tensor, row_pos: torch.Tensor,
-                row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_rank: int, rot: int, window: int, scale: float) -> None:
+                row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_rank: int, rot: int, window: int, scale: float,
+                sink: Optional[torch.Tensor] = None) -> None:
     """Attention over cached latents, one warp a (row, head): a [rows, heads, kv_rank + rot] are the absorbed queries, every head
     reads the same ``c_pages`` [pages, 1, 64, kv_rank] (keys and values at once) and ``r_pages`` [pages, 1, 64, rot];
     out [rows, heads, kv_rank] = sum_j softmax_j((a_c . c_j + a_r . r_j) * scale) c_j over the positions j the row sees
-    (``window`` > 0: the last ``window`` ones, itself included).  Rows whose slot is negative give zeros."""
+    (``window`` > 0: the last ``window`` ones, itself included).  ``sink`` float32 [heads]: every head's softmax has one more term
+    e^sink in its denominator, without a key or a value.  Rows whose slot is negative give zeros."""
     _need(a, "a")
+    _sink_values(sink, heads, "latent_rows")
     _need(c_pages, "c_pages", a.dtype)
     _need(out, "out", a.dtype)
     _need(page_table, "page_table", torch.int32)
@@ -1089,7 +1169,7 @@ def latent_rows(a: torch.Tensor, c_pages: torch.Tensor, r_pages: Optional[torch.
     _bounds_paged("latent_rows", rows, row_pos, row_slot, page_table, c_pages.shape[0])
     _call(_fn("bc_latent_rows_" + _suffix(a.dtype)), _ptr(a), _ptr(c_pages), _ptr(r_pages if rot > 0 else None), _ptr(page_table), _ptr(row_pos),
           _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_rank), _c_int(rot), _c_int(page_table.shape[1]), _c_int(c_pages.shape[0]),
-          _c_int(window), _c_float(scale), _stream())
+          _c_int(window), _c_float(scale), _ptr(sink), _stream())
 
 
 def latent_values(ctx: torch.Tensor, w_uv: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, heads: int, kv_rank: int, value_dim: int) -> None:
@@ -1131,13 +1211,14 @@ def latent_decode_splits(rows: int, heads: int, reach: int, window: int, kv_rank
 
 def latent_decode(a: torch.Tensor, c_pages: torch.Tensor, r_pages: Optional[torch.Tensor], page_table: torch.Tensor, row_pos: torch.Tensor,
                   row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_rank: int, rot: int, window: int, scale: float,
-                  splits: Optional[int] = None, reach: Optional[int] = None) -> None:
+                  splits: Optional[int] = None, reach: Optional[int] = None, sink: Optional[torch.Tensor] = None) -> None:
     """What latent_rows computes, for bf16 and few rows: a block takes (row, sixteen heads, split of the cached positions), the
     heads sharing every read of the cache on mma.sync tiles; several splits are merged in their order by a second kernel.
     The result does not depend on ``reach``, only the number of splits chosen does."""
     for t, name in ((a, "a"), (c_pages, "c_pages"), (out, "out")):
         _need(t, name, torch.bfloat16)
     _need(page_table, "page_table", torch.int32)
+    _sink_values(sink, heads, "latent_decode")
     rows = a.shape[0]
     if a.numel() != rows * heads * (kv_rank + rot) or out.numel() != rows * heads * kv_rank or c_pages.shape[-1] != kv_rank:
         raise KernelError(f"latent_decode: a {tuple(a.shape)}, out {tuple(out.shape)}, pages {tuple(c_pages.shape)} do not fit")
@@ -1152,7 +1233,7 @@ def latent_decode(a: torch.Tensor, c_pages: torch.Tensor, r_pages: Optional[torc
     _bounds_paged("latent_decode", rows, row_pos, row_slot, page_table, c_pages.shape[0])
     _call(_fn("bc_latent_decode_bf16"), _ptr(a), _ptr(c_pages), _ptr(r_pages if rot > 0 else None), _ptr(page_table), _ptr(row_pos), _ptr(row_slot),
           _ptr(out), _ptr(scratch), _c_int(rows), _c_int(heads), _c_int(kv_rank), _c_int(rot), _c_int(page_table.shape[1]), _c_int(c_pages.shape[0]),
-          _c_int(window), _c_float(scale), _c_int(splits), _stream())
+          _c_int(window), _c_float(scale), _c_int(splits), _ptr(sink), _stream())
 
 
 def latent_heads(q: torch.Tensor, cos_sin: Optional[torch.Tensor], row_pos: torch.Tensor, out: torch.Tensor, heads: int, dim: int, rot: int) -> None:
@@ -1272,6 +1353,17 @@ def relu2(z: torch.Tensor, out: torch.Tensor) -> None:
     _call(_fn("bc_relu2_" + _suffix(out.dtype)), _ptr(z), _ptr(out), ctypes.c_longlong(z.numel()), _stream())
 
 
+def glu_clipped(z: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out[r, j] = g sigmoid(alpha g) (u + 1) with g = min(z[r, j], limit) and u = clamp(z[r, F + j], -limit, limit): z float32
+    [rows, 2 F] (a gate/up product's sums), out [rows, F] of any type the kernels know."""
+    _need(z, "z", torch.float32)
+    _need(out, "out")
+    rows, F = out.shape
+    if tuple(z.shape) != (rows, 2 * F):
+        raise KernelError(f"glu_clipped: z is {tuple(z.shape)}, wanted {(rows, 2 * F)}")
+    _call(_fn("bc_glu_clipped_" + _suffix(out.dtype)), _ptr(z), _ptr(out), _c_int(rows), _c_int(F), _c_float(limit), _c_float(alpha), _stream())
+
+
 def gated_add(h: torch.Tensor, g: torch.Tensor, y: torch.Tensor, residual: torch.Tensor) -> None:
     """residual[r] += sigmoid(g . h[r]) * y[r]: h [rows, K] and g [K] of one type, y and residual float32 [rows, E]."""
     _need(h, "h")
@@ -1305,6 +1397,22 @@ def softcap(scores: torch.Tensor, cap: float) -> None:
     """scores <- cap * tanh(scores / cap), in place; float32."""
     _need(scores, "scores", torch.float32)
     _call(_fn("bc_softcap_f32"), _ptr(scores), ctypes.c_longlong(scores.numel()), _c_float(cap), _stream())
+
+
+def scale_scores(scores: torch.Tensor, factor: float) -> None:
+    """scores <- factor * scores, in place; float32."""
+    _need(scores, "scores", torch.float32)
+    _call(_fn("bc_scale_f32"), _ptr(scores), ctypes.c_longlong(scores.numel()), _c_float(factor), _stream())
+
+
+def add_bias(x: torch.Tensor, b: torch.Tensor) -> None:
+    """x[r] += b: x float32 [rows, E], b float32 [E] (the bias of a product whose epilogue adds into x)."""
+    _need(x, "x", torch.float32)
+    _need(b, "b", torch.float32)
+    rows, E = x.shape
+    if b.numel() != E:
+        raise KernelError(f"add_bias: {b.numel()} biases for rows of {E}")
+    _call(_fn("bc_add_bias_f32"), _ptr(x), _ptr(b), _c_int(rows), _c_int(E), _stream())
 
 
 def reentry(x: torch.Tensor, x0: torch.Tensor, step: torch.Tensor, cat: torch.Tensor) -> None:
@@ -1465,9 +1573,12 @@ def attention_tiles(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cac
     """Causal attention of every sequence's new rows (many, or one) against its cached positions on mma.sync
     tiles, bf16, with values of their own width, a sliding window and/or a chunk mask (``chunk`` > 0: a position
     sees only those of its own chunk of that many positions, counted from position 0).  ``sink`` adds one to the
-    softmax's denominator (a position of score 0 without a value); ``out_scale`` multiplies the result."""
+    softmax's denominator (a position of score 0 without a value), or, given as a float32 tensor [heads], e^sink[head];
+    ``out_scale`` multiplies the result."""
     for t, name in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache"), (out, "out")):
         _need(t, name, torch.bfloat16)
+    if isinstance(sink, torch.Tensor):
+        _sink_values(sink, heads, "attention_tiles")
     for t, name in ((page_table, "page_table"), (seq_rows, "seq_rows"), (seq_slot, "seq_slot"), (seq_start, "seq_start")):
         _need(t, name, torch.int32)
     if out.shape[1] != heads * value_dim:
@@ -1482,7 +1593,7 @@ def attention_tiles(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cac
     _call(_fn("bc_attention_prefill_sink_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
           _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
           _c_int(value_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk), _c_float(scale),
-          _c_int(1 if sink else 0), _c_float(out_scale), _stream())
+          _c_int(0 if sink is None or sink is False else 1), _ptr(sink if isinstance(sink, torch.Tensor) else None), _c_float(out_scale), _stream())
 
 
 def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Optional[torch.Tensor] = None, q_stride: int = 0,
@@ -1507,8 +1618,11 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
     other head sizes on mma.sync tiles, 64 rows a block.  ``use_tc`` forces one or the other.
     ``chunk`` > 0: a position sees only those of its own chunk of that many positions, counted from position 0.
     ``value_dim`` (default ``head_dim``): the width of a head's values, in v_cache and in out.
-    ``sink`` adds one to the softmax's denominator (a position of score 0 without a value); ``out_scale`` multiplies the result."""
+    ``sink`` adds one to the softmax's denominator (a position of score 0 without a value), or, given as a float32 tensor [heads],
+    e^sink[head]; ``out_scale`` multiplies the result."""
     value_dim = head_dim if value_dim is None else int(value_dim)
+    if isinstance(sink, torch.Tensor):
+        _sink_values(sink, heads, "attention_prefill")
     _need(q, "q", torch.bfloat16)
     _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16)
@@ -1539,9 +1653,10 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
         _call(_fn("bc_attention_prefill_tc_sink_bf16"), _ptr(q), _c_int(q_stride), _c_int(out.shape[0]), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
               _ptr(seq_rows), _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads),
               _c_int(head_dim), _c_int(value_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_int(chunk),
-              _c_float(scale), _c_int(1 if sink else 0), _c_float(out_scale), _stream())
+              _c_float(scale), _c_int(0 if sink is None or sink is False else 1), _ptr(sink if isinstance(sink, torch.Tensor) else None),
+              _c_float(out_scale), _stream())
         return
-    if chunk > 0 or value_dim != head_dim or sink or out_scale != 1.0:
+    if chunk > 0 or value_dim != head_dim or (sink is not None and sink is not False) or out_scale != 1.0:
         attention_tiles(q, q_stride, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, heads, kv_heads, head_dim,
                         value_dim, window=window, chunk=chunk, scale=scale, sink=sink, out_scale=out_scale)
         return

@@ -178,11 +178,13 @@ class CacheNeed:
     one plane (1, width); planes may differ in shape.  ``window`` > 0 if only that many
     latest positions are ever read; ``chunk`` > 0 if a position only ever reads those of its
     own chunk of that many positions (counted from position 0), so that whole chunks behind
-    the newest one can be let go.  Runs with equal needs share one storage group."""
+    the newest one can be let go.  ``keep_first`` > 0 if the first that many positions of a sequence stay readable
+    whatever the window (they are never let go).  Runs with equal needs share one storage group."""
 
     planes: Tuple[Tuple[int, int], ...]
     window: int = 0
     chunk: int = 0
+    keep_first: int = 0
 
     def __post_init__(self):
         self.planes = tuple((int(h), int(w)) for h, w in self.planes)
@@ -190,13 +192,14 @@ class CacheNeed:
             raise ValueError(f"a cache need wants at least one plane of positive sizes, got {self.planes}")
 
     @staticmethod
-    def keys_values(kv_heads: int, head_dim: int, window: int = 0, value_dim: Optional[int] = None, chunk: int = 0) -> "CacheNeed":
+    def keys_values(kv_heads: int, head_dim: int, window: int = 0, value_dim: Optional[int] = None, chunk: int = 0,
+                    keep_first: int = 0) -> "CacheNeed":
         """Keys of ``kv_heads`` heads of ``head_dim`` a position, and values of ``value_dim``
         (default: the same width)."""
-        return CacheNeed(((kv_heads, head_dim), (kv_heads, head_dim if value_dim is None else value_dim)), window, chunk)
+        return CacheNeed(((kv_heads, head_dim), (kv_heads, head_dim if value_dim is None else value_dim)), window, chunk, keep_first)
 
     def key(self) -> Tuple:
-        return (self.planes, self.window, self.chunk)
+        return (self.planes, self.window, self.chunk, self.keep_first)
 
     def values_per_token(self) -> int:
         return sum(h * w for h, w in self.planes)

@@ -9,8 +9,8 @@ inputs are per-sequence state.  The feed-forward (and its norm) may be left out;
 without a norm of its own reads what the mixer reads, x += mixer(h) + feed_forward(h) with
 h = norm1(x).
 
-The sandwich block: a norm before and after each sublayer, x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))).
-The second half may be left out."""
+The sandwich block: a norm before and after each sublayer, x += norm1b(mixer(conv(norm1(x)))); x += norm2b(ff(norm2(x))).
+The second half may be left out, and so may the short convolution (or token shift) of the mixer's input."""
 
 from __future__ import annotations
 
@@ -93,8 +93,8 @@ class SandwichBlock(Block):
     """Every sublayer's result passes a norm of its own before it joins the stream, so no product can add into the stream
     itself: the sublayer adds into a cleared float buffer, and one kernel norms that and adds it."""
 
-    ROLES = {"norm1": NORMS, "mixer": MIXERS, "norm1b": NORMS, "norm2": NORMS, "feed_forward": FEED_FORWARDS, "norm2b": NORMS}
-    OPTIONAL = ("norm2", "feed_forward", "norm2b")
+    ROLES = {"norm1": NORMS, "conv": CONVOLUTIONS, "mixer": MIXERS, "norm1b": NORMS, "norm2": NORMS, "feed_forward": FEED_FORWARDS, "norm2b": NORMS}
+    OPTIONAL = ("conv", "norm2", "feed_forward", "norm2b")
 
     def __init__(self, parts, hidden_size: int):
         super().__init__(parts, hidden_size)
@@ -104,11 +104,30 @@ class SandwichBlock(Block):
             if getattr(self, role) is not None and type(getattr(self, role)) is not RMSNorm:
                 raise ValueError(f"the norm after a sublayer ('{role}') must be a plain RMS norm")
 
+    def state_needs(self) -> Dict[str, StateNeed]:
+        needs = super().state_needs()
+        need = None if self.conv is None else self.conv.state_need()
+        if need is not None:
+            needs["conv"] = need
+        return needs
+
     def forward(self, residual: torch.Tensor, ctx: StepContext, mem: RunMemory, rt: Runtime) -> None:
         rows = residual.shape[0]
         h = torch.empty((rows, self.hidden_size), dtype=rt.dtype, device=residual.device)
         y = torch.zeros((rows, self.hidden_size), dtype=torch.float32, device=residual.device)
-        self.norm1.forward(residual, h)
+        if self.conv is not None and ctx.decode and type(self.norm1) is RMSNorm and isinstance(self.conv, CausalConvResidual):
+            # Single rows: the convolution over the mixer's input rides in the norm's kernel.
+            tail = mem.states.get("conv")
+            if tail is None:
+                raise RuntimeError("the convolution was given no state: the cache does not serve this block")
+            ops.norm_pair(residual, self.norm1.weight, None, h, None, self.norm1.eps, self.conv.weight_t,
+                          tail if self.conv.taps > 1 else tail[:, :0], ctx.row_slot, write_tail=mem.writes)
+        else:
+            self.norm1.forward(residual, h)
+            if self.conv is not None:
+                hc = torch.empty_like(h)
+                self.conv.forward(h, hc, ctx, mem.states.get("conv"), mem.writes)
+                h = hc
         self.mixer.forward(h, y, ctx, mem)
         if self.feed_forward is None:
             ops.norm_add(y, self.norm1b.weight, residual, self.norm1b.eps)

@@ -37,12 +37,12 @@ class TokenEmbedding(Embedding):
 class LinearHead(Head):
     """Scores = x W^T in float32.  A tied head has no tensor of its own and multiplies by
     the embedding table (model.rs:200); a folder that still stores one is tolerated.
-    ``softcap`` > 0 bounds the scores: s <- softcap * tanh(s / softcap)."""
+    ``scale`` multiplies the scores (1: as they are); ``softcap`` > 0 then bounds them: s <- softcap * tanh(s / softcap)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False, tensor: str = "weight", softcap: float = 0.0):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied=tied, tensor=tensor, softcap=softcap)
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False, tensor: str = "weight", softcap: float = 0.0, scale: float = 1.0):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied=tied, tensor=tensor, softcap=softcap, scale=scale)
         self.vocab_size, self.hidden_size, self.tied, self.tensor = int(vocab_size), int(hidden_size), bool(tied), str(tensor)
-        self.softcap = float(softcap)
+        self.softcap, self.scale = float(softcap), float(scale)
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
@@ -57,5 +57,7 @@ class LinearHead(Head):
         if w is None:
             raise RuntimeError("a tied head needs the embedding's table")
         products.linear(x, w, out, products.EPI_STORE_F32, "head product")
+        if self.scale != 1.0:
+            ops.scale_scores(out, self.scale)
         if self.softcap > 0.0:
             ops.softcap(out, self.softcap)

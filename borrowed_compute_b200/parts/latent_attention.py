@@ -14,9 +14,16 @@ for all heads and never expanded.  With many rows a sequence (prompts) what the 
 into every head's keys and values, and the prompt attention kernels of the other mixers run over those.
 
 Parameters: a sliding ``window`` (0: every earlier position), the score ``scale`` (default (dim + rot_dim)^-1/2), the
-position encoding of the rotated part (a PartSpec-like mapping; {"kind": "none"} with ``rot_dim`` 0), and ``own_kv``:
+position encoding of the rotated part (a PartSpec-like mapping; {"kind": "none"} with ``rot_dim`` 0), ``own_kv``:
 False for a mixer without a down projection to c and r, whose run reads another run's cache (RunSpec.memory_of) with
-its own Wuk and Wuv.  Tensor names after the prefix: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o.
+its own Wuk and Wuv, and ``sink``: every head's softmax has one more term e^sink_n in its denominator, a learned number a
+head (tensor ``sink``) that has no key and no value, so that a row's weights add up to less than one.
+Tensor names after the prefix: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o, sink.
+
+A position encoding that pairs neighbours, (2i, 2i + 1), needs no kernel of its own: a score is a sum over the rotated
+dimensions, so the same permutation of them on the query's and on the key's side leaves it as it is.  The rows of Wuq and of
+Wdkv that make the rotated parts are reordered once, when the weights are loaded, so that pair i sits at (i, i + rot_dim / 2),
+and the kernels rotate those; the cache then keeps r in that order, which only this mixer reads.
 """
 
 from __future__ import annotations
@@ -74,9 +81,10 @@ def seen_pages(ctx: StepContext, window: int, device: torch.device):
 class LatentAttention(Mixer):
     def __init__(self, hidden_size: int, heads: int, head_dim: int, value_dim: int, q_rank: int, kv_rank: int, norm_eps: float,
                  rot_dim: int = 0, position: Optional[Mapping[str, Any]] = None, scale: Optional[float] = None, window: int = 0,
-                 own_kv: bool = True):
+                 own_kv: bool = True, sink: bool = False):
         super().__init__(hidden_size=hidden_size, heads=heads, head_dim=head_dim, value_dim=value_dim, q_rank=q_rank, kv_rank=kv_rank,
-                         norm_eps=norm_eps, rot_dim=rot_dim, position=position, scale=scale, window=window, own_kv=own_kv)
+                         norm_eps=norm_eps, rot_dim=rot_dim, position=position, scale=scale, window=window, own_kv=own_kv, sink=sink)
+        self.has_sink = bool(sink)
         self.hidden_size, self.heads, self.head_dim, self.value_dim = int(hidden_size), int(heads), int(head_dim), int(value_dim)
         self.q_rank, self.kv_rank, self.rot_dim, self.window = int(q_rank), int(kv_rank), int(rot_dim), int(window)
         self.norm_eps, self.own_kv = float(norm_eps), bool(own_kv)
@@ -91,8 +99,7 @@ class LatentAttention(Mixer):
         rotated = int(getattr(self.position, "head_dim", 0))
         if rotated != self.rot_dim:
             raise ValueError(f"the position encoding rotates {rotated} dimensions, the mixer's rotated part has {self.rot_dim}")
-        if self.rot_dim and getattr(self.position, "pairing", "half") != "half":
-            raise ValueError("latent attention rotates pairs (i, i + rot_dim / 2)")
+        self.adjacent = bool(self.rot_dim) and getattr(self.position, "pairing", "half") == "adjacent"
 
     def tensors(self) -> Dict[str, TensorSpec]:
         e, H = self.hidden_size, self.heads
@@ -102,6 +109,8 @@ class LatentAttention(Mixer):
                "g": TensorSpec((H, e)), "o": TensorSpec((e, H * self.value_dim))}
         if self.own_kv:
             out.update({"dkv": TensorSpec((self.kv_rank + self.rot_dim, e)), "dkv.norm": TensorSpec((self.kv_rank,), role="vector", init="ones")})
+        if self.has_sink:
+            out["sink"] = TensorSpec((H,), role="vector")
         return out
 
     def cache_need(self) -> Optional[CacheNeed]:
@@ -110,6 +119,16 @@ class LatentAttention(Mixer):
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         super().load(tensors, rt)
+        if self.adjacent:
+            # Neighbouring pairs (2i, 2i + 1) moved to (i, i + rot_dim / 2), on the query's side and on the key's alike.
+            tensors = dict(tensors)
+            D, ROT, H = self.head_dim, self.rot_dim, self.heads
+            order = torch.cat([torch.arange(0, ROT, 2), torch.arange(1, ROT, 2)]).to(tensors["uq"].device)
+            uq = tensors["uq"].reshape(H, D + ROT, self.q_rank)
+            tensors["uq"] = torch.cat([uq[:, :D], uq[:, D:][:, order]], dim=1).reshape(H * (D + ROT), self.q_rank)
+            if self.own_kv:
+                tensors["dkv"] = torch.cat([tensors["dkv"][: self.kv_rank], tensors["dkv"][self.kv_rank:][order]], dim=0)
+        self.sink = tensors["sink"].reshape(-1).contiguous() if self.has_sink else None
         down = [tensors["dq"]] + ([tensors["dkv"]] if self.own_kv else []) + [tensors["g"]]
         self.w_down = torch.cat(down, dim=0).contiguous()
         self.kv_at = self.q_rank if self.own_kv else -1
@@ -158,9 +177,10 @@ class LatentAttention(Mixer):
             found = torch.empty((rows, H, R), dtype=x.dtype, device=dev)
             if path == "split":
                 ops.latent_decode(a, c_pages, r_pages, mem.page_table, ctx.row_pos, ctx.row_slot, found, H, R, ROT, self.window, self.scale,
-                                  reach=ctx.max_total)
+                                  reach=ctx.max_total, sink=self.sink)
             else:
-                ops.latent_rows(a, c_pages, r_pages, mem.page_table, ctx.row_pos, ctx.row_slot, found, H, R, ROT, self.window, self.scale)
+                ops.latent_rows(a, c_pages, r_pages, mem.page_table, ctx.row_pos, ctx.row_slot, found, H, R, ROT, self.window, self.scale,
+                                sink=self.sink)
             ops.latent_values(found, self.w_uv, gate, att, H, R, DV)
         products.linear(att, self.w_o, residual, products.EPI_ADD_F32, "output product")
 
@@ -187,5 +207,5 @@ class LatentAttention(Mixer):
             ops.latent_spread(kv, seen_r, keys, values, H, D, DV, ROT)
             scratch_table = ints[3][: ctx.seqs * widest].view(ctx.seqs, widest)
             ops.attention_prefill(qh, H * KP, keys, values, scratch_table, ctx.seq_rows, ints[4], ints[5], found, ctx.seqs, ctx.max_new, H, H, KP,
-                                  window=self.window, scale=self.scale, value_dim=VP)
+                                  window=self.window, scale=self.scale, value_dim=VP, sink=self.sink)
         ops.latent_gate(found, gate, att, H, DV)

@@ -8,6 +8,7 @@ from typing import Dict
 
 import torch
 
+from .. import ops
 from . import products
 from .base import FEED_FORWARDS, FeedForward, Runtime, StepContext, TensorSpec
 
@@ -65,4 +66,38 @@ class PlainMLP(FeedForward):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         products.linear(x, self.w_up, act, products.EPI_RELU2, "up product")
+        products.linear(act, self.w_down, residual, products.EPI_ADD_F32, "down product")
+
+
+@FEED_FORWARDS.register("clipped_glu")
+class ClippedGLU(FeedForward):
+    """down( g sigmoid(alpha g) (u + 1) ) with g = min(gate x, limit) and u = clamp(up x, -limit, limit): a gated feed-forward
+    whose gate saturates from above, whose up branch is bounded on both sides and carries a one.  Gate and up are one product
+    with float sums; the activation works on those and rounds once."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702, gate: str = "gate", up: str = "up",
+                 down: str = "down"):
+        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, limit=limit, alpha=alpha, gate=gate, up=up, down=down)
+        self.hidden_size, self.intermediate_size, self.limit, self.alpha = int(hidden_size), int(intermediate_size), float(limit), float(alpha)
+        if self.limit <= 0.0:
+            raise ValueError(f"the bound of a clipped gate must be positive, got {limit}")
+        self.names = (str(gate), str(up), str(down))
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        e, f = self.hidden_size, self.intermediate_size
+        gate, up, down = self.names
+        return {gate: TensorSpec((f, e)), up: TensorSpec((f, e)), down: TensorSpec((e, f))}
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().load(tensors, rt)
+        gate, up, down = self.names
+        self.w_gate_up = torch.cat([tensors[gate], tensors[up]], dim=0).contiguous()      # gate rows, then up rows
+        self.w_down = tensors[down].contiguous()
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        rows, F = x.shape[0], self.intermediate_size
+        z = torch.empty((rows, 2 * F), dtype=torch.float32, device=x.device)
+        products.linear(x, self.w_gate_up, z, products.EPI_STORE_F32, "gate/up product")
+        act = torch.empty((rows, F), dtype=x.dtype, device=x.device)
+        ops.glu_clipped(z, act, self.limit, self.alpha)
         products.linear(act, self.w_down, residual, products.EPI_ADD_F32, "down product")

@@ -2,7 +2,7 @@
 that every row uses.
 
 Router scores are sigmoid(W_router h) (or a softmax over the experts) in float; the ``top`` largest choose a row's
-experts and are its weights, as they are or divided by their sum (``renormalize``).  The weight multiplies the
+experts and are its weights, as they are or divided by their sum (``renormalize``), times ``weight_factor``.  The weight multiplies the
 expert's input (``weight_on="input"``: the sum over the chosen experts of expert(w h)) or its output.  An expert is
 down( silu(gate x) * (up x) ).
 
@@ -35,10 +35,11 @@ force_simt = False      # tests: the CUDA-core products (the checked twin) for b
 class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, experts: int, top: int, intermediate_size: int, shared_size: int = 0, score: str = "sigmoid",
                  renormalize: bool = False, weight_on: str = "input", router: str = "learned", expert: str = "swiglu", shared_gate: bool = False,
-                 vocab_size: int = 0):
+                 vocab_size: int = 0, weight_factor: float = 1.0):
         super().__init__(hidden_size=hidden_size, experts=experts, top=top, intermediate_size=intermediate_size, shared_size=shared_size,
                          score=score, renormalize=renormalize, weight_on=weight_on, router=router, expert=expert, shared_gate=shared_gate,
-                         vocab_size=vocab_size)
+                         vocab_size=vocab_size, weight_factor=weight_factor)
+        self.weight_factor = float(weight_factor)
         self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
         self.intermediate_size, self.shared_size = int(intermediate_size), int(shared_size)
         if not 0 < self.top <= self.experts or self.top > 16:
@@ -49,6 +50,8 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"router {router!r} must be 'learned' or 'table', expert {expert!r} 'swiglu' or 'relu2'")
         self.softmax, self.renormalize, self.on_input = score == "softmax", bool(renormalize), weight_on == "input"
         self.by_table, self.gated, self.shared_gate, self.vocab_size = router == "table", expert == "swiglu", bool(shared_gate), int(vocab_size)
+        if self.by_table and self.weight_factor != 1.0:
+            raise ValueError("experts named by a table weigh 1 / top each and take no factor")
         if self.by_table and (self.vocab_size <= 0 or self.on_input):
             raise ValueError("experts named by a table want the vocabulary's size and their weights on the output")
         if not self.gated and self.on_input:
@@ -96,7 +99,8 @@ class RoutedExperts(FeedForward):
             ops.moe_table_route(self.table, ctx.tokens, ctx.row_slot, choice, weight, E)
         else:
             logits = torch.empty((rows, E), dtype=torch.float32, device=dev)
-            ops.moe_route(x, self.router, ctx.row_slot, logits, choice, weight, softmax=self.softmax, renorm=self.renormalize)
+            ops.moe_route(x, self.router, ctx.row_slot, logits, choice, weight, softmax=self.softmax, renorm=self.renormalize,
+                          factor=self.weight_factor)
         # bfloat16 whose widths the tensor cores take: the rows are gathered in sorted order (times their weights: the weight
         # multiplies the expert's input) and both products run on tcgen05 tiles; else on the CUDA cores, gathering as they go.
         tensor_cores = not force_simt and self.intermediate_size % 8 == 0 and ops.gemm_tc_grouped_accepts(x, self.w_gate_up)

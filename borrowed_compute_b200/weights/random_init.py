@@ -141,6 +141,8 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype, de
         return torch.ones(spec.shape, dtype=dtype, device=device)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=dtype, device=device)
+    if spec.init == "identity":
+        return torch.eye(spec.shape[0], spec.shape[1], dtype=dtype, device=device)
     key = tensor_key(seed, name)
     if torch.device(device).type == "cuda":
         return _normal_on_device(spec.shape, key, dtype, device)
