@@ -211,6 +211,326 @@ talk_rows_kernel(const T* q, const T* k_cache, const T* v_cache, const int* __re
     }
 }
 
+// -------------------------------------------------------------------------------------- tiles
+// bf16 prompts.  A block owns sixteen rows of one sequence and all heads; warp w owns heads w, w + warps, .. (HPW of them).
+// Positions come in tiles of 32 (half a page), keys and values of every kv head, through two stages of shared memory by
+// cp.async.  A tile takes two passes with a barrier between them:
+//   1. every warp multiplies its heads' queries with the tile's keys on m16n8k16 tiles, scales, bounds, and leaves the raw
+//      scores (float) in shared memory;
+//   2. every warp mixes its heads' scores out of all heads' raw ones (float), masks, takes the softmax's step (running maximum
+//      and sum in registers), and multiplies the weights (bf16, out of its own registers) with the tile's values.
+// The tiles a block walks: those of the kept first positions that lie before the window of its last row, then those from the
+// window of its first row to its last row's own position.
+#define TT_KEYS 32
+#define TT_ROWS 16
+#define TT_RS 40            // floats a row of raw scores takes in shared memory: 64-bit reads of a quarter-warp's rows meet no bank twice
+
+__device__ __forceinline__ float tt_bound(float s, float cap, float two_over_cap) {
+    // cap * tanh(s / cap) = cap * (1 - 2 / (e^(2 s / cap) + 1))
+    const float e = __expf(s * two_over_cap);
+    return cap * (1.0f - __fdividef(2.0f, e + 1.0f));
+}
+
+template <int D, int HPW>
+__global__ void __launch_bounds__(512)
+talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const int* __restrict__ page_table,
+                  const int* __restrict__ seq_rows, const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const float* gate,
+                  const float* __restrict__ temp, const float* __restrict__ talk, bf16* __restrict__ out, int H, int G, int max_pages, int n_pages,
+                  int window, int keep_first, float scale, float cap, int stages) {
+    constexpr int CHUNKS = D / 8, KD = D / 16, ND = D / 8;
+    constexpr int HEAD_BYTES = TT_KEYS * D * 2;            // one kv head's 32 positions
+    extern __shared__ __align__(128) uint8_t tt_smem[];
+    const int plane = G * HEAD_BYTES;                      // a tile's keys of all kv heads; its values follow
+    float* raw = reinterpret_cast<float*>(tt_smem + (size_t)stages * 2 * plane);      // [H][16][TT_RS]
+    float* mix = raw + (size_t)H * TT_ROWS * TT_RS;        // [H][H]
+
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(q); PDL_FRESH(k_cache); PDL_FRESH(v_cache); PDL_FRESH(gate);
+    const int sq = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int gq = lane >> 2, tq = lane & 3, j4 = lane >> 3, r8 = lane & 7;
+    const int slot = seq_slot[sq];
+    const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
+    const int n_tiles_q = (n_new + TT_ROWS - 1) / TT_ROWS;
+    const int q_tile = n_tiles_q - 1 - (int)blockIdx.x;    // the last rows see the most: they go first
+    if (slot < 0 || q_tile < 0) return;
+    const int start = seq_start[sq];
+    const int tok0 = q_tile * TT_ROWS, tok_end = min(n_new, tok0 + TT_ROWS);
+    const int* pages = page_table + (size_t)slot * max_pages;
+    const int group = H / G;
+    const int last_pos = start + n_new - 1;                // the last position the sequence holds after this step
+
+    for (int i = threadIdx.x; i < H * H; i += blockDim.x) mix[i] = talk[i];
+    auto first_seen = [&](int p) { return window > 0 && p + 1 > window ? p + 1 - window : 0; };
+    int pos[2], lo[2];
+    bool live[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int tok = tok0 + gq + 8 * i;
+        live[i] = tok < n_new;
+        pos[i] = start + tok;
+        lo[i] = first_seen(pos[i]);
+    }
+    // The block's tiles of positions: [0, kept) and [win_begin, win_end], as one stretch where they meet.
+    const int p_first = start + tok0, p_last = start + tok_end - 1;
+    int kept = (min(keep_first, first_seen(p_last)) + TT_KEYS - 1) / TT_KEYS;
+    const int win_begin = first_seen(p_first) / TT_KEYS, win_end = p_last / TT_KEYS;
+    if (kept >= win_begin) kept = win_begin;
+    const int n_tiles = kept + (win_end - win_begin + 1);
+    auto tile_at = [&](int k) { return k < kept ? k : win_begin + (k - kept); };
+    auto page_of = [&](int tile) {
+        const int pi = tile / 2;
+        const int page = pi < max_pages ? pages[pi] : -1;
+        return page >= 0 && page < n_pages ? page : -1;
+    };
+    auto load_tile = [&](int tile, int stage) {
+        const int page = page_of(tile);
+        if (page < 0) return;
+        const uint32_t kb = ad_smem(tt_smem + (size_t)stage * 2 * plane), vb = kb + plane;
+        const int per_head = TT_KEYS * CHUNKS;
+        for (int i = threadIdx.x; i < G * per_head; i += blockDim.x) {
+            const int g = i / per_head, rest = i - g * per_head, row = rest / CHUNKS, c = rest - row * CHUNKS;
+            const size_t src = (((size_t)page * G + g) * BC_PAGE + (tile & 1) * TT_KEYS + row) * D + c * 8;
+            cp_async16(kb + g * HEAD_BYTES + tile_offset<D>(row, c), k_cache + src);
+            cp_async16(vb + g * HEAD_BYTES + tile_offset<D>(row, c), v_cache + src);
+        }
+    };
+
+    // This warp's heads: queries as fragments, what each score is multiplied by, and the sums that run over the tiles.
+    uint32_t qf[HPW][KD][4];
+    float o[HPW][ND][4], m[HPW][2], l[HPW][2], factor[HPW];
+#pragma unroll
+    for (int a = 0; a < HPW; a++) {
+        const int h = warp + a * warps;
+        factor[a] = h < H ? scale * temp[h] : 0.0f;
+#pragma unroll
+        for (int kd = 0; kd < KD; kd++)
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const bf16* qr = q + ((size_t)(row0 + tok0 + gq + 8 * i) * H + (h < H ? h : 0)) * D + kd * 16 + 2 * tq;
+                const bool ok = live[i] && h < H;
+                qf[a][kd][i] = ok ? *reinterpret_cast<const uint32_t*>(qr) : 0u;
+                qf[a][kd][i + 2] = ok ? *reinterpret_cast<const uint32_t*>(qr + 8) : 0u;
+            }
+#pragma unroll
+        for (int nd = 0; nd < ND; nd++) o[a][nd][0] = o[a][nd][1] = o[a][nd][2] = o[a][nd][3] = 0.0f;
+        m[a][0] = m[a][1] = -INFINITY;
+        l[a][0] = l[a][1] = 0.0f;
+    }
+    const float two_over_cap = cap > 0.0f ? 2.0f / cap : 0.0f;
+    const float LOG2E = 1.4426950408889634f;
+
+    if (n_tiles > 0) load_tile(tile_at(0), 0);
+    cp_async_commit();
+    for (int it = 0; it < n_tiles; it++) {
+        const int stage = stages > 1 ? (it & 1) : 0;
+        if (stages == 1 && it > 0) {
+            __syncthreads();                               // everybody has left the tile before
+            load_tile(tile_at(it), 0);
+            cp_async_commit();
+        }
+        cp_async_wait<0>();
+        __syncthreads();
+        if (stages > 1 && it + 1 < n_tiles) load_tile(tile_at(it + 1), stage ^ 1);
+        cp_async_commit();
+        const int tile = tile_at(it);
+        if (page_of(tile) < 0) continue;                   // a tile without a page is neither fetched nor multiplied
+        const uint32_t kb = ad_smem(tt_smem + (size_t)stage * 2 * plane), vb = kb + plane;
+        if (tile == last_pos / TT_KEYS && last_pos % TT_KEYS != TT_KEYS - 1) {
+            // What lies past the sequence's last position belongs to nobody (a sequence that held the page before may have left
+            // not-a-numbers there, and 0 x NaN is NaN in the product with the values): those value rows are cleared in the copy.
+            const int first = last_pos % TT_KEYS + 1;
+            for (int i = threadIdx.x; i < G * (TT_KEYS - first) * CHUNKS; i += blockDim.x) {
+                const int g = i / ((TT_KEYS - first) * CHUNKS), rest = i - g * (TT_KEYS - first) * CHUNKS;
+                *reinterpret_cast<uint4*>(tt_smem + (size_t)stage * 2 * plane + plane + g * HEAD_BYTES + tile_offset<D>(first + rest / CHUNKS, rest % CHUNKS)) =
+                    make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncthreads();
+        }
+        // 1. raw scores of this warp's heads
+#pragma unroll
+        for (int a = 0; a < HPW; a++) {
+            const int h = warp + a * warps;
+            if (h >= H) continue;
+            const uint32_t kh = kb + (h / group) * HEAD_BYTES;
+            float s[4][4];
+#pragma unroll
+            for (int nb = 0; nb < 4; nb++) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+#pragma unroll
+            for (int kd = 0; kd < KD; kd++)
+#pragma unroll
+                for (int np = 0; np < 2; np++) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(kh + tile_offset<D>(np * 16 + (j4 >> 1) * 8 + r8, kd * 2 + (j4 & 1)), b0, b1, b2, b3);
+                    mma_16816(s[2 * np], qf[a][kd], b0, b1);
+                    mma_16816(s[2 * np + 1], qf[a][kd], b2, b3);
+                }
+            float* rh = raw + (size_t)h * TT_ROWS * TT_RS;
+#pragma unroll
+            for (int nb = 0; nb < 4; nb++)
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    float v0 = s[nb][2 * i] * factor[a], v1 = s[nb][2 * i + 1] * factor[a];
+                    if (cap > 0.0f) v0 = tt_bound(v0, cap, two_over_cap), v1 = tt_bound(v1, cap, two_over_cap);
+                    *reinterpret_cast<float2*>(rh + (gq + 8 * i) * TT_RS + nb * 8 + 2 * tq) = make_float2(v0, v1);
+                }
+        }
+        __syncthreads();
+        // 2. this warp's heads: the mix of all heads' raw scores, the softmax's step, the product with the values
+#pragma unroll
+        for (int a = 0; a < HPW; a++) {
+            const int h = warp + a * warps;
+            if (h >= H) continue;
+            float s[4][4];
+#pragma unroll
+            for (int nb = 0; nb < 4; nb++) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+            const float* mh = mix + (size_t)h * H;
+            for (int mm = 0; mm < H; mm++) {
+                const float f = mh[mm];
+                const float* rm = raw + (size_t)mm * TT_ROWS * TT_RS;
+#pragma unroll
+                for (int nb = 0; nb < 4; nb++)
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const float2 v = *reinterpret_cast<const float2*>(rm + (gq + 8 * i) * TT_RS + nb * 8 + 2 * tq);
+                        s[nb][2 * i] = fmaf(f, v.x, s[nb][2 * i]);
+                        s[nb][2 * i + 1] = fmaf(f, v.y, s[nb][2 * i + 1]);
+                    }
+            }
+            float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nb = 0; nb < 4; nb++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int i = e >> 1;
+                    const int t = tile * TT_KEYS + nb * 8 + 2 * tq + (e & 1);
+                    const bool seen = live[i] && t <= pos[i] && (t >= lo[i] || t < keep_first);
+                    s[nb][e] = seen ? s[nb][e] * LOG2E : -INFINITY;
+                    tmax[i] = fmaxf(tmax[i], s[nb][e]);
+                }
+            float corr[2], base[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
+                tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
+                const float mn = fmaxf(m[a][i], tmax[i]);
+                corr[i] = mn == -INFINITY ? 1.0f : fast_exp2(m[a][i] - mn);
+                base[i] = mn == -INFINITY ? 0.0f : mn;
+                m[a][i] = mn;
+            }
+            float psum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int nb = 0; nb < 4; nb++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    s[nb][e] = fast_exp2(s[nb][e] - base[e >> 1]);
+                    psum[e >> 1] += s[nb][e];
+                }
+            l[a][0] = l[a][0] * corr[0] + psum[0];
+            l[a][1] = l[a][1] * corr[1] + psum[1];
+#pragma unroll
+            for (int nd = 0; nd < ND; nd++) {
+                o[a][nd][0] *= corr[0]; o[a][nd][1] *= corr[0]; o[a][nd][2] *= corr[1]; o[a][nd][3] *= corr[1];
+            }
+            const uint32_t vh = vb + (h / group) * HEAD_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++) {
+                const uint32_t pf[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                                        pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+                for (int nd = 0; nd < ND; nd += 2) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(vh + tile_offset<D>(kk * 16 + (j4 & 1) * 8 + r8, nd + (j4 >> 1)), b0, b1, b2, b3);
+                    mma_16816(o[a][nd], pf, b0, b1);
+                    mma_16816(o[a][nd + 1], pf, b2, b3);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int a = 0; a < HPW; a++) {
+        const int h = warp + a * warps;
+        if (h >= H) continue;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            float sum = l[a][i];
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if (!live[i]) continue;
+            const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+            const size_t at = ((size_t)(row0 + tok0 + gq + 8 * i) * H + h) * D + 2 * tq;
+#pragma unroll
+            for (int nd = 0; nd < ND; nd++) {
+                const float2 gv = *reinterpret_cast<const float2*>(gate + at + nd * 8);
+                *reinterpret_cast<uint32_t*>(out + at + nd * 8) = pack_bf16(o[a][nd][2 * i] * inv * gv.x, o[a][nd][2 * i + 1] * inv * gv.y);
+            }
+        }
+    }
+}
+
+static size_t tt_smem_bytes(int H, int G, int D, int stages) {
+    return (size_t)stages * 2 * G * TT_KEYS * D * 2 + ((size_t)H * TT_ROWS * TT_RS + (size_t)H * H) * sizeof(float);
+}
+// Heads a warp takes: one up to sixteen heads, two up to thirty-two; a warp's accumulators hold HPW * D value columns.
+static int tt_heads_per_warp(int H) { return H <= 16 ? 1 : 2; }
+
+extern "C" int bc_talk_tiles_accepts(int H, int G, int D) {
+    if (H <= 0 || G <= 0 || H % G || H > 32 || D % 16 || D < 16 || D > 128 || tt_heads_per_warp(H) * D > 128) return 0;
+    return tt_smem_bytes(H, G, D, 1) <= 200 * 1024;
+}
+
+template <int D, int HPW>
+static int tiles_go(const void* q, const void* k_cache, const void* v_cache, const int* page_table, const int* seq_rows, const int* seq_slot,
+                    const int* seq_start, const float* gate, const float* temp, const float* talk, void* out, int seqs, int max_new, int H, int G,
+                    int max_pages, int n_pages, int window, int keep_first, float scale, float cap, cudaStream_t s) {
+    const int stages = tt_smem_bytes(H, G, D, 2) <= 200 * 1024 ? 2 : 1;
+    const size_t smem = tt_smem_bytes(H, G, D, stages);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(talk_tiles_kernel<D, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            bc_set_error("talk_tiles: cannot set shared memory to %zu: %s", smem, cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = smem;
+    }
+    const int warps = (H + HPW - 1) / HPW;
+    bc_launch(talk_tiles_kernel<D, HPW>, dim3((max_new + TT_ROWS - 1) / TT_ROWS, seqs), dim3(32 * warps), smem, s, (const bf16*)q, (const bf16*)k_cache,
+              (const bf16*)v_cache, page_table, seq_rows, seq_slot, seq_start, gate, temp, talk, (bf16*)out, H, G, max_pages, n_pages, window, keep_first,
+              scale, cap, stages);
+    BC_LAUNCH_STATUS();
+}
+
+// q: [rows, H D] bf16; k_cache, v_cache: [pages, G, BC_PAGE, D] bf16; gate: [rows, H D] float; temp: [H]; talk: [H, H]; out: [rows, H D] bf16.
+// Sequence s brings rows seq_rows[s] .. seq_rows[s + 1] and held seq_start[s] positions before.
+extern "C" int bc_talk_tiles_bf16(const void* q, const void* k_cache, const void* v_cache, const int* page_table, const int* seq_rows, const int* seq_slot,
+                                  const int* seq_start, const float* gate, const float* temp, const float* talk, void* out, int seqs, int max_new, int H,
+                                  int G, int D, int max_pages, int n_pages, int window, int keep_first, float scale, float cap, cudaStream_t s) {
+    BC_CHECK_ARG(bc_talk_tiles_accepts(H, G, D), "talk_tiles: %d heads on %d of %d are not taken (up to 32 heads, heads of multiples of 16 up to 128, "
+                 "up to 64 with more than 16 heads)", H, G, D);
+    BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && window >= 0 && keep_first >= 0 && cap >= 0.0f && temp && talk && gate,
+                 "talk_tiles: bad sizes seqs=%d max_new=%d window=%d kept=%d", seqs, max_new, window, keep_first);
+    if (seqs == 0 || max_new == 0) return BC_OK;
+#define TT_GO(DD, HH) return tiles_go<DD, HH>(q, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, gate, temp, talk, out, seqs, max_new, H, G, \
+                                              max_pages, n_pages, window, keep_first, scale, cap, s)
+    const int hpw = tt_heads_per_warp(H);
+    switch (D) {
+        case 16: if (hpw == 1) TT_GO(16, 1); TT_GO(16, 2);
+        case 32: if (hpw == 1) TT_GO(32, 1); TT_GO(32, 2);
+        case 48: if (hpw == 1) TT_GO(48, 1); TT_GO(48, 2);
+        case 64: if (hpw == 1) TT_GO(64, 1); TT_GO(64, 2);
+        case 80: TT_GO(80, 1);
+        case 96: TT_GO(96, 1);
+        case 112: TT_GO(112, 1);
+        case 128: TT_GO(128, 1);
+    }
+#undef TT_GO
+    bc_set_error("talk_tiles: heads of %d are not taken", D);
+    return BC_ERR_ARG;
+}
+
 // ---------------------------------------------------------------------------------- launchers
 template <class T>
 static int prepare(const float* proj, int rows, int P, int g_at, const float* bias, const float* cos_sin, int table_positions, const int* row_pos,

@@ -966,6 +966,32 @@ def talk_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pag
           _c_int(k_cache.shape[0]), _c_int(window), _c_int(keep_first), _c_float(scale), _c_float(cap), _stream())
 
 
+def talk_tiles_accepts(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tile kernel for prompts takes these sizes (bf16; up to 16 heads of a multiple of 16 up to 128, or up to 32 heads of
+    up to 64, and a tile of all kv heads' keys and values that fits shared memory).  Otherwise talk_rows serves."""
+    return dtype == torch.bfloat16 and bool(_fn("bc_talk_tiles_accepts")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim)))
+
+
+def talk_tiles(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, seq_rows: torch.Tensor, seq_slot: torch.Tensor,
+               seq_start: torch.Tensor, gate: torch.Tensor, temp: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
+               heads: int, kv_heads: int, head_dim: int, window: int, keep_first: int, scale: float, cap: float) -> None:
+    """What talk_rows computes, for bf16 prompts on mma.sync tiles: a block owns sixteen rows of one sequence and all heads, so that
+    every head can mix its score out of all heads' raw scores; sequence s brings rows seq_rows[s] .. seq_rows[s + 1] and held
+    seq_start[s] positions before."""
+    _talk_check("talk_tiles", q, k_cache, v_cache, gate, temp, talk, out, heads, kv_heads, head_dim)
+    _need(q, "q", torch.bfloat16)
+    for t, name in ((page_table, "page_table"), (seq_rows, "seq_rows"), (seq_slot, "seq_slot"), (seq_start, "seq_start")):
+        _need(t, name, torch.int32)
+    if seq_rows.numel() < seqs + 1 or seq_slot.numel() < seqs or seq_start.numel() < seqs:
+        raise KernelError("talk_tiles: fewer sequence entries than sequences")
+    _bounds("talk_tiles: seq_slot", seq_slot, page_table.shape[0], seqs, lowest=-1)
+    _bounds("talk_tiles: seq_rows", seq_rows, out.shape[0] + 1, seqs + 1)
+    _bounds("talk_tiles: page_table", page_table, k_cache.shape[0], lowest=-1)
+    _call(_fn("bc_talk_tiles_bf16"), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows), _ptr(seq_slot), _ptr(seq_start), _ptr(gate),
+          _ptr(temp), _ptr(talk), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_table.shape[1]),
+          _c_int(k_cache.shape[0]), _c_int(window), _c_int(keep_first), _c_float(scale), _c_float(cap), _stream())
+
+
 # ------------------------------------------------------------------------------ routed experts
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, row_slot: Optional[torch.Tensor], logits: torch.Tensor, choice: torch.Tensor,

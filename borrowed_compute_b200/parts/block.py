@@ -123,7 +123,10 @@ class SandwichBlock(Block):
             ops.norm_pair(residual, self.norm1.weight, None, h, None, self.norm1.eps, self.conv.weight_t,
                           tail if self.conv.taps > 1 else tail[:, :0], ctx.row_slot, write_tail=mem.writes)
         else:
-            self.norm1.forward(residual, h)
+            if self.conv is not None and type(self.norm1) is RMSNorm:
+                ops.norm_pair(residual, self.norm1.weight, None, h, None, self.norm1.eps)      # the same sums as in a step of single rows
+            else:
+                self.norm1.forward(residual, h)
             if self.conv is not None:
                 hc = torch.empty_like(h)
                 self.conv.forward(h, hc, ctx, mem.states.get("conv"), mem.writes)

@@ -78,7 +78,7 @@ class TalkingAttention(Mixer):
         self.position.load({}, rt)
 
     def path(self, ctx: StepContext, dtype: torch.dtype) -> str:
-        tiles = hasattr(ops, "talk_tiles_accepts") and ops.talk_tiles_accepts(self.heads, self.kv_heads, self.head_dim, dtype)
+        tiles = ops.talk_tiles_accepts(self.heads, self.kv_heads, self.head_dim, dtype)
         if force == "rows" or (force == "tiles" and tiles):
             return force
         return "tiles" if tiles and not ctx.decode and ctx.max_new > 1 else "rows"

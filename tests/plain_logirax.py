@@ -28,6 +28,8 @@ Output: N(x) with ``final.norm``, scores = embed N(x) * logit_scale; rows enter 
 
 from __future__ import annotations
 
+import math
+
 import numpy as np
 
 
@@ -219,3 +221,171 @@ def greedy(cfg, t, prompt, n):
     for _ in range(n):
         tokens.append(int(forward(cfg, t, tokens)[-1].argmax()))
     return tokens[len(prompt):]
+
+
+# ------------------------------------------------------------------ models for the tests
+
+def to_bf16(a):
+    """Rounds to the nearest value that bfloat16 holds (ties to even), as float64."""
+    f = np.ascontiguousarray(a, dtype=np.float32)
+    u = f.view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32).reshape(f.shape).astype(np.float64)
+
+
+def talking_mixer(heads, kv_heads, dim, size, keep_first, rot_dims, softcap=15.0, scale=None, base=10000.0):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": scale or 1.5 / math.sqrt(dim), "softcap": softcap,
+         "mask": {"size": size, "keep_first": keep_first}}
+    if rot_dims:
+        m["rot"] = {"base": base, "dims": rot_dims}
+    return m
+
+
+def latent_mixer(heads, dim, vdim, q_rank, kv_rank, rot_dim, scale=None, base=2000.0):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "rot_dim": rot_dim,
+         "scale": scale or 1.0 / math.sqrt(dim + rot_dim)}
+    if rot_dim:
+        m["rot"] = {"base": base, "dims": rot_dim}
+    return m
+
+
+def dense(ff, limit):
+    return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+def moe(experts, top, ff, shared, scale):
+    f = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": scale}, "expert": {"ff": ff}}
+    if shared:
+        f["shared"] = {"ff": shared}
+    return f
+
+
+def model(vocab, width, layers, eps=1e-5, embedding_scale=1.0, logit_scale=1.0):
+    return {"architecture": "Logirax", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embedding_scale},
+            "logit_scale": logit_scale,
+            "layers": [{"type": "attention" if "kv_heads" in m else "latent_attention", "mixer": m, "mlp": f} for m, f in layers]}
+
+
+# Two small models that differ in every size and constant, in the order of their layers and in what they leave out.
+SMALL = {
+    "A": model(176, 64, [
+        (talking_mixer(4, 2, 16, 24, 3, 8), moe(6, 2, 24, 16, 1.5)),
+        (latent_mixer(3, 16, 24, 24, 40, 8), dense(48, 1.0)),
+        (talking_mixer(4, 2, 16, 24, 3, 8), None),
+        (latent_mixer(3, 16, 24, 24, 40, 8), moe(6, 2, 24, 16, 1.5)),
+    ], eps=1e-5, embedding_scale=8.0, logit_scale=0.5),
+    "B": model(97, 40, [
+        (latent_mixer(2, 8, 8, 16, 16, 0), moe(3, 3, 8, 0, 1.0)),
+        (talking_mixer(6, 6, 20, 70, 0, 20, softcap=0.0, base=300.0), dense(24, 0.5)),
+        (talking_mixer(3, 1, 32, 9, 70, 0, softcap=4.0), moe(5, 1, 16, 8, 2.5)),
+    ], eps=1e-6, embedding_scale=1.0, logit_scale=3.0),
+}
+
+
+def tensor_shapes(cfg):
+    """name -> shape of every tensor a model of this configuration has."""
+    E, out = cfg["width"], {"embed": (cfg["vocab"], cfg["width"]), "final.norm": (cfg["width"],)}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        out.update({p + "norm1": (E,), p + "norm1b": (E,), p + "shift": (E,)})
+        if L["type"] == "attention":
+            H, G, d = m["heads"], m["kv_heads"], m["dim"]
+            out.update({p + "mix.q": (H * d, E), p + "mix.q.b": (H * d,), p + "mix.k": (G * d, E), p + "mix.k.b": (G * d,), p + "mix.talk": (H, H),
+                        p + "mix.temp": (H,), p + "mix.g": (H * d, E), p + "mix.o": (E, H * d), p + "mix.o.b": (E,)})
+        else:
+            H, d, dv, QR, R, rd = m["heads"], m["dim"], m["vdim"], m["q_rank"], m["kv_rank"], m["rot_dim"]
+            out.update({p + "mix.dq": (QR, E), p + "mix.dq.norm": (QR,), p + "mix.uq": (H * (d + rd), QR), p + "mix.dkv": (R + rd, E),
+                        p + "mix.dkv.norm": (R,), p + "mix.uk": (H * d, R), p + "mix.uv": (H * dv, R), p + "mix.sink": (H,), p + "mix.g": (H, E),
+                        p + "mix.o": (E, H * dv)})
+        f = L.get("mlp")
+        if f:
+            out.update({p + "norm2": (E,), p + "norm2b": (E,)})
+            if f["kind"] == "dense":
+                out.update({p + "mlp.gate": (f["ff"], E), p + "mlp.up": (f["ff"], E), p + "mlp.down": (E, f["ff"])})
+            else:
+                ff = f["expert"]["ff"]
+                for e in range(f["router"]["experts"]):
+                    out.update({f"{p}mlp.e{e}.gate": (ff, E), f"{p}mlp.e{e}.up": (ff, E), f"{p}mlp.e{e}.down": (E, ff)})
+                out[p + "mlp.router"] = (f["router"]["experts"], E)
+                if f.get("shared"):
+                    s = f["shared"]["ff"]
+                    out.update({p + "mlp.shared.gate": (s, E), p + "mlp.shared.up": (s, E), p + "mlp.shared.down": (E, s)})
+    return out
+
+
+def make_weights(cfg, seed):
+    """Random weights that bfloat16 holds exactly: matrices of spread 1 / sqrt(inputs) (gates and routers wider, so that they
+    decide), norm weights and shifts around zero, heads' temperatures around one, a mix of heads near the identity, sinks that
+    weigh about as much as a key."""
+    rng = np.random.default_rng(seed)
+    t = {}
+    for name, shape in tensor_shapes(cfg).items():
+        last = name.split(".")[-1]
+        if "norm" in name:
+            a = 0.2 * rng.standard_normal(shape)
+        elif last == "shift":
+            a = rng.uniform(-0.2, 0.9, shape)
+        elif last == "temp":
+            a = rng.uniform(0.6, 1.6, shape)
+        elif last == "talk":
+            a = np.eye(shape[0]) + 0.4 * rng.standard_normal(shape) / math.sqrt(shape[0])
+        elif last == "sink":
+            a = rng.uniform(-1.0, 3.0, shape)
+        elif last == "b":
+            a = 0.3 * rng.standard_normal(shape)
+        elif name == "embed":
+            a = rng.standard_normal(shape)
+        else:
+            a = rng.standard_normal(shape) / math.sqrt(shape[-1]) * (3.0 if last in ("router", "g", "gate") else 1.0)
+        t[name] = to_bf16(a)
+    return t
+
+
+def draw_config(rng):
+    """A configuration whose sizes, constants and order of layers are drawn."""
+    E = int(rng.choice([24, 40, 64, 72]))
+    layers = []
+    for _ in range(int(rng.integers(2, 5))):
+        if rng.random() < 0.5:
+            G = int(rng.choice([1, 2, 3]))
+            H = G * int(rng.choice([1, 2, 3]))
+            d = int(rng.choice([8, 12, 16, 32, 40]))
+            rot = int(rng.choice([0, d // 2 // 2 * 2, d]))
+            m = talking_mixer(H, G, d, int(rng.choice([1, 5, 33, 64, 100])), int(rng.choice([0, 1, 4, 66])), rot,
+                              softcap=float(rng.choice([0.0, 5.0, 30.0])), base=float(rng.choice([100.0, 10000.0])))
+        else:
+            rd = int(rng.choice([0, 4, 8, 16]))
+            m = latent_mixer(int(rng.choice([1, 2, 5])), int(rng.choice([8, 16, 24])), int(rng.choice([8, 16, 40])), int(rng.choice([8, 12, 24])),
+                             int(rng.choice([8, 16, 20, 48])), rd, base=float(rng.choice([50.0, 50000.0])))
+        kind = rng.random()
+        if kind < 0.2:
+            f = None
+        elif kind < 0.5:
+            f = dense(int(rng.choice([8, 20, 48])), float(rng.choice([0.5, 1.0, 7.0])))
+        else:
+            n = int(rng.choice([1, 3, 8]))
+            f = moe(n, int(rng.integers(1, n + 1)), int(rng.choice([8, 12, 32])), int(rng.choice([0, 8, 24])), float(rng.choice([1.0, 2.5])))
+        layers.append((m, f))
+    return model(int(rng.choice([50, 131, 200])), E, layers, eps=float(rng.choice([1e-6, 1e-5, 1e-3])),
+                 embedding_scale=float(rng.choice([1.0, 4.0, 12.0])), logit_scale=float(rng.choice([0.5, 1.0, 2.0])))
+
+
+def router_margin(cfg, t, tokens):
+    """The smallest gap between the last chosen and the first left-out router score over every row and layer of one sequence
+    (infinite without routers): a sequence with a wide gap chooses the same experts under bfloat16 rounding."""
+    t = {k: np.asarray(v, dtype=np.float64) for k, v in t.items()}
+    x = t["embed"][np.asarray(tokens)] * float(cfg.get("embedding", {}).get("scale", 1.0))
+    gap, eps = math.inf, float(cfg["norm"]["eps"])
+    for i, L in enumerate(cfg["layers"]):
+        f, p = L.get("mlp"), f"l{i}."
+        h = token_shift(offset_norm(x, t[p + "norm1"], eps), t[p + "shift"])
+        mix = talking_attention if L["type"] == "attention" else latent_attention
+        x = x + offset_norm(mix(h, L["mixer"], t, p + "mix.", eps), t[p + "norm1b"], eps)
+        if f:
+            h2 = offset_norm(x, t[p + "norm2"], eps)
+            if f["kind"] == "moe" and f["router"]["top"] < f["router"]["experts"]:
+                s = np.sort(sigmoid(h2 @ t[p + "mlp.router"].T), axis=1)[:, ::-1]
+                k = f["router"]["top"]
+                gap = min(gap, float((s[:, k - 1] - s[:, k]).min()))
+            x = x + offset_norm(feed_forward(h2, f, t, p + "mlp."), t[p + "norm2b"], eps)
+    return gap
