@@ -824,6 +824,107 @@ def bench_fudelorn(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps
     return _bench_models(configs, costs_of, c["vocab"], out, pk, rng, FP32_TFLOPS, batch, prompt, steps, warmup)
 
 
+def logirax_config(width, heads, dim, rot, wdim, vdim, q_rank, kv_rank, window, ff, experts, top, expert_ff, shared, vocab, layers):
+    """Layers in turn: attention whose heads talk (a quarter as many kv heads, heads of ``wdim``, half of their dimensions turning,
+    a window that keeps the first four positions) with a dense feed-forward whose gate is clipped, then latent attention with a
+    sink and routed experts plus a shared one."""
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": wdim, "vdim": wdim, "scale": wdim ** -0.5, "softcap": 30.0,
+                     "mask": {"size": window, "keep_first": 4}, "rot": {"base": 10000.0, "dims": wdim // 2}}
+            out.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}})
+            continue
+        mixer = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": (dim + rot) ** -0.5,
+                 "rot": {"base": 500000.0, "dims": rot}}
+        out.append({"type": "latent_attention", "mixer": mixer,
+                    "mlp": {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "scale": 1.5}, "shared": {"ff": shared}}})
+    return {"architecture": "Logirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "logit_scale": 1.0, "layers": out}
+
+
+def logirax_costs(c, layers, batch, ctx_len, T) -> dict:
+    """What each kernel class of the Logirax model has to move in a decode step (bytes) and to compute in a prompt step of T tokens
+    (operations, or bytes where it only moves data), summed over the model's layers.  The latent layers' classes are Fudelorn's
+    (a rotating layer that keeps its own cache); the talking layers read, a row, at most a window and the kept positions of two
+    planes (keys, and the keys as projected), and mix heads * heads raw scores a (row, position) on the CUDA cores."""
+    E, H, DV, QR, R, W, V = c["width"], c["heads"], c["vdim"], c["q_rank"], c["kv_rank"], c["window"], c["vocab"]
+    X, k, f, fs, F, B = c["experts"], c["top"], c["expert_ff"], c["shared"], c["ff"], batch
+    D, G = c["wdim"], max(1, c["heads"] // 4)
+    d, rot = c["dim"], c["rot"]
+    nt, nl = (layers + 1) // 2, layers // 2               # talking layers (dense feed-forward), latent layers (experts)
+    touched = X * (1.0 - (1.0 - k / X) ** B)
+    P = QR + H + R + rot                                  # rows of the latent layers' fused down projection
+    Pt = (2 * H + G) * D                                  # rows of the talking layers' fused projection [q | k | gate]
+    seen_t = min(ctx_len + 1, W + 4)
+    seen_l = ctx_len + 1
+    pairs_t = sum(min(t + 1, W + 4) for t in range(T))
+    pairs_l = T * (T + 1) / 2.0
+    pages = -(-T // 64)
+    decode = {
+        "qkv product": nt * (2.0 * Pt * E + B * (2.0 * E + 4.0 * Pt)),
+        "talk prepare": nt * B * (4.0 * Pt + 2.0 * H * D + 4.0 * G * D + 4.0 * H * D),
+        "talking attention": nt * B * (seen_t * G * D * 4.0 + 2.0 * H * D + 4.0 * H * D + 2.0 * H * D),
+        "bias": nt * B * E * 8.0,
+        "latent down product": nl * (2.0 * P * E + B * (2.0 * E + 4.0 * P)),
+        "latent norm + append": nl * B * (4.0 * P + 2.0 * QR + 4.0 * H + 2.0 * (R + rot)),
+        "query up product": nl * (2.0 * H * (d + rot) * QR + B * (2.0 * QR + 4.0 * H * (d + rot))),
+        "latent query": nl * (2.0 * H * d * R + B * (4.0 * H * (d + rot) + 2.0 * H * (R + rot))),
+        "attention": nl * B * (seen_l * (R + rot) * 2.0 + 2.0 * H * (R + rot) + 2.0 * H * R),
+        "latent values": nl * (2.0 * H * DV * R + B * (2.0 * H * R + 4.0 * H + 2.0 * H * DV)),
+        "norm": layers * 2 * (B * E * 6.0 + E * 4.0 + B * E * 12.0 + E * 4.0) + B * E * 6.0,
+        "output product": nt * (2.0 * H * D * E + B * (2.0 * H * D + 8.0 * E)) + nl * (2.0 * H * DV * E + B * (2.0 * H * DV + 8.0 * E)),
+        "gate/up product": nt * (4.0 * E * F + B * (2.0 * E + 2.0 * F)) + nl * (4.0 * E * fs + B * (2.0 * E + 2.0 * fs)),
+        "down product": nt * (2.0 * E * F + B * (2.0 * F + 8.0 * E)) + nl * (2.0 * E * fs + B * (2.0 * fs + 8.0 * E)),
+        "routing": nl * (X * E * 4.0 + B * (2.0 * E + X * 4.0 + k * 8.0)),
+        "expert sort": nl * B * k * 16.0,
+        "expert gather": nl * B * k * E * 4.0,
+        "expert sum": nl * (B * k * E * 4.0 + B * E * 8.0),
+        "expert product": nl * (touched * 3.0 * f * E * 2.0 + B * k * (2.0 * E + 4.0 * f + 4.0 * E)),
+        "head product": 2.0 * V * E + B * (2.0 * E + 4.0 * V),
+    }
+    prefill = {
+        "qkv product": ("flops", nt * 2.0 * T * Pt * E),
+        "talk prepare": ("bytes", nt * T * (4.0 * Pt + 2.0 * H * D + 4.0 * G * D + 4.0 * H * D)),
+        # tensor-core operations (scores and values); the mix of heads * heads raw scores a pair is CUDA-core work on top of it
+        "talking attention": ("flops", nt * 4.0 * H * D * pairs_t),
+        "bias": ("bytes", nt * T * E * 8.0),
+        "short convolution": ("bytes", layers * T * E * 4.0),
+        "latent down product": ("flops", nl * 2.0 * T * P * E),
+        "latent norm + append": ("bytes", nl * T * (4.0 * P + 2.0 * QR + 4.0 * H + 2.0 * (R + rot))),
+        "query up product": ("flops", nl * 2.0 * T * H * (d + rot) * QR),
+        "latent query": ("bytes", nl * T * H * (d + rot) * 6.0),
+        "latent keys and values": ("bytes", nl * pages * 64 * (4.0 * (R + rot) + 4.0 * H * (d + DV) + 2.0 * H * rot)),
+        "key and value up product": ("flops", nl * 2.0 * pages * 64 * H * (d + DV) * R),
+        "attention": ("flops", nl * 2.0 * H * (d + rot + DV) * pairs_l),
+        "latent values": ("bytes", nl * T * H * DV * 4.0),
+        "norm": ("bytes", layers * 2 * T * E * 18.0),
+        "output product": ("flops", 2.0 * T * E * (nt * H * D + nl * H * DV)),
+        "gate/up product": ("flops", 4.0 * T * E * (nt * F + nl * fs)),
+        "down product": ("flops", 2.0 * T * E * (nt * F + nl * fs)),
+        "routing": ("bytes", nl * T * (2.0 * E + X * 4.0 + k * 8.0)),
+        "expert sort": ("bytes", nl * T * k * 16.0),
+        "expert gather": ("bytes", nl * T * k * E * 4.0),
+        "expert sum": ("bytes", nl * T * (k * E * 4.0 + E * 8.0)),
+        "expert product": ("flops", nl * 2.0 * T * k * 3.0 * f * E),
+    }
+    return {"decode": decode, "prefill": prefill}
+
+
+def bench_logirax(pk, rng, size="wide", layers=4, batch=8, prompt=PROMPT, steps=32, warmup=4) -> dict:
+    """Prompt and decode throughput of a Logirax model of ``layers`` layers at sizes that resemble a real model's layers (random
+    weights), beside a Fudelorn model, the closest of the other designs (sandwich blocks, latent attention, experts), of the same
+    width, heads, latents, feed-forward widths, vocabulary and depth; every kernel class of both against its own bytes or operations."""
+    c = FUDELORN_SIZES[size]
+    configs = {"logirax": logirax_config(layers=layers, **c), "fudelorn": fudelorn_config(layers=layers, **c)}
+    out = {"size": size, "sizes": c, "layers": layers, "batch": batch, "prompt": prompt,
+           "between": "weights of a step exceed the L2", "peaks": pk, "fp32_cuda_core_tflops_nominal": round(FP32_TFLOPS, 1)}
+
+    def costs_of(name, cfg):
+        return (logirax_costs if name == "logirax" else fudelorn_costs)(c, layers, batch, prompt + 2, prompt)
+
+    return _bench_models(configs, costs_of, c["vocab"], out, pk, rng, FP32_TFLOPS, batch, prompt, steps, warmup)
+
+
 def run_ours(args) -> dict:
     import numpy as np
     import torch
@@ -982,9 +1083,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the two other shapes")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-class timing of one decode and one prompt step")
-    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny", "fegidra", "pozirax", "fudelorn"],
+    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny", "fegidra", "pozirax", "fudelorn", "logirax"],
                     help="run one of the further workloads alone and print its figures (not the default run's one JSON line)")
-    ap.add_argument("--size", default="wide", choices=sorted(FEGIDRA_SIZES), help="with --point fegidra, pozirax or fudelorn: which sizes")
+    ap.add_argument("--size", default="wide", choices=sorted(FEGIDRA_SIZES), help="with --point fegidra, pozirax, fudelorn or logirax: which sizes")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py or pyproject) "
@@ -1003,7 +1104,8 @@ def main() -> int:
                "tiny": lambda: bench_tiny(rng),
                "fegidra": lambda: bench_fegidra(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup),
                "pozirax": lambda: bench_pozirax(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup),
-               "fudelorn": lambda: bench_fudelorn(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup)}[args.point]
+               "fudelorn": lambda: bench_fudelorn(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup),
+               "logirax": lambda: bench_logirax(peaks(), rng, args.size, args.layers or 4, args.batch, args.prompt, min(args.steps, 32), args.warmup)}[args.point]
         print(json.dumps({"point": args.point, **one()}))
         return 0
     print(json.dumps(run_ours(args)))

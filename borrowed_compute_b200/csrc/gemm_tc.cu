@@ -54,6 +54,7 @@ struct TcParams {
     int n_tiles, t_tiles;   // blocks along the weight rows and along the tokens
     int pair_tokens;        // the paired kernel: tokens a tile (64, 128, 192 or 256)
     int starve;             // test hook: the first stage expects 16 bytes that never come, so a bounded wait runs out
+    float glu_limit, glu_alpha;   // SwiGLU: a positive limit bounds gate and up and puts alpha into the gate's sigmoid (see glu_mul)
     long long* trace;       // measurement builds (-DBC_TC_TRACE): sixteen time stamps a block, else null
 };
 
@@ -275,7 +276,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (n >= p.N) return;
                 float r[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : epi_plain<EPI>(__uint_as_float(v[j]));
+                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? glu_mul(__uint_as_float(v[j]), __uint_as_float(u[j]), p.glu_limit, p.glu_alpha) : epi_plain<EPI>(__uint_as_float(v[j]));
                 const int t_first = t0 + c0;
                 const size_t o = (size_t)t_first * p.N + n;
 #pragma unroll
@@ -352,7 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (EPI == EPI_STORE || EPI == EPI_RELU2) ((bf16*)p.out)[o] = __float2bfloat16_rn(epi_plain<EPI>(v));
                     if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = v;
                     if (EPI == EPI_ADD_F32) ((float*)p.out)[o] += v;   // one owner an element: no reduction needed (and measured 0.4 % of a step faster than a fire-and-forget one)
-                    if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(v, u));
+                    if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(glu_mul(v, u, p.glu_limit, p.glu_alpha));
                 }
             };
             // A read of a peer's shared memory takes up to half a microsecond when all blocks of
@@ -590,7 +591,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (out_n >= p.N) return;
                 float r[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : epi_plain<EPI>(__uint_as_float(v[j]));
+                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? glu_mul(__uint_as_float(v[j]), __uint_as_float(u[j]), p.glu_limit, p.glu_alpha) : epi_plain<EPI>(__uint_as_float(v[j]));
                 const int t_first = t0 + c0;
                 const size_t o = (size_t)t_first * p.N + out_n;
 #pragma unroll
@@ -888,8 +889,8 @@ extern "C" void bc_gemm_tc_set_trace(long long* buf, int launches) { g_tc_trace 
 // X [T, K] bf16, W [N, K] bf16 (SwiGLU: [2N, K], gate rows then up rows); out [T, N] bf16 or
 // float by epilogue.  K must be a multiple of 8 (a TMA row stride is a multiple of 16
 // bytes); pointers 16-byte aligned.  splits > 1 needs the workspace above.
-extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, int N, int K, int epilogue, int splits, float* partial,
-                               int* counters, cudaStream_t s) {
+static int gemm_tc_go(const void* X, const void* W, void* out, int T, int N, int K, int epilogue, int splits, float* partial, int* counters,
+                      float glu_limit, float glu_alpha, cudaStream_t s) {
     BC_CHECK_ARG(T >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
     BC_CHECK_ARG(K % 8 == 0, "gemm_tc: K=%d is not a multiple of 8 (TMA needs 16-byte row strides); use the CUDA-core product", K);
     BC_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
@@ -920,6 +921,8 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     p.pair_tokens = 256;
     p.starve = paired ? 0 : g_tc_starve;
     if (!paired) g_tc_starve = 0;
+    p.glu_limit = glu_limit;
+    p.glu_alpha = glu_alpha;
     p.trace = nullptr;
 #ifdef BC_TC_TRACE
     if (!paired && g_tc_trace && g_tc_trace_next < g_tc_trace_launches) p.trace = g_tc_trace + (size_t)(g_tc_trace_next++) * 1024 * 16;
@@ -941,6 +944,17 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
         case EPI_RELU2: return launch_bn<EPI_RELU2>(bn, stack, mw, mx, p, splits, s);
     }
     return BC_ERR_ARG;
+}
+
+extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, int N, int K, int epilogue, int splits, float* partial,
+                               int* counters, cudaStream_t s) {
+    return gemm_tc_go(X, W, out, T, N, K, epilogue, splits, partial, counters, 0.0f, 1.0f, s);
+}
+// The gated product (EPI_SWIGLU) with bounds: out = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
+extern "C" int bc_gemm_tc_glu_bf16(const void* X, const void* W, void* out, int T, int N, int K, int splits, float* partial, int* counters,
+                                   float limit, float alpha, cudaStream_t s) {
+    BC_CHECK_ARG(limit > 0.0f, "gemm_tc: the bound of a gated product must be positive, got %g", (double)limit);
+    return gemm_tc_go(X, W, out, T, N, K, EPI_SWIGLU, splits, partial, counters, limit, alpha, s);
 }
 
 // ------------------------------------------------------------ the product over groups of rows

@@ -19,8 +19,12 @@
 //
 // Scores, the bound, the mix, the softmax's weights and all sums are float.  A row's sums run in an order that its position
 // and the sizes alone fix, so a row gives the same bits in any batch and under any cut of its prompt.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "mma_tiles.cuh"
+
+namespace cg = cooperative_groups;
 
 #define TA_MAX_HEADS 64
 #define TA_MAX_D 256
@@ -221,6 +225,11 @@ talk_rows_kernel(const T* q, const T* k_cache, const T* v_cache, const int* __re
 //      and sum in registers), and multiplies the weights (bf16, out of its own registers) with the tile's values.
 // The tiles a block walks: those of the kept first positions that lie before the window of its last row, then those from the
 // window of its first row to its last row's own position.
+// More than sixteen heads are shared out over a thread-block cluster of CL blocks (two up to 32 heads, four up to 64): a block
+// owns H / CL heads and their kv heads (so a tile's keys and values are loaded once a cluster) and writes its heads' raw scores into
+// every block's shared memory (distributed shared memory: one remote write an element, where reading the others' scores in place
+// would be H / CL remote reads of each), so that every block mixes its heads' scores out of a copy of its own; the two barriers a
+// tile are then the cluster's.
 #define TT_KEYS 32
 #define TT_ROWS 16
 #define TT_RS 40            // floats a row of raw scores takes in shared memory: 64-bit reads of a quarter-warp's rows meet no bank twice
@@ -231,18 +240,28 @@ __device__ __forceinline__ float tt_bound(float s, float cap, float two_over_cap
     return cap * (1.0f - __fdividef(2.0f, e + 1.0f));
 }
 
-template <int D, int HPW>
+template <int D, int HPW, int CL>
 __global__ void __launch_bounds__(512)
 talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const int* __restrict__ page_table,
                   const int* __restrict__ seq_rows, const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const float* gate,
                   const float* __restrict__ temp, const float* __restrict__ talk, bf16* __restrict__ out, int H, int G, int max_pages, int n_pages,
-                  int window, int keep_first, float scale, float cap, int stages) {
+                  int window, int keep_first, float scale, float cap, int stages, float* __restrict__ scratch, int splits) {
     constexpr int CHUNKS = D / 8, KD = D / 16, ND = D / 8;
     constexpr int HEAD_BYTES = TT_KEYS * D * 2;            // one kv head's 32 positions
     extern __shared__ __align__(128) uint8_t tt_smem[];
-    const int plane = G * HEAD_BYTES;                      // a tile's keys of all kv heads; its values follow
-    float* raw = reinterpret_cast<float*>(tt_smem + (size_t)stages * 2 * plane);      // [H][16][TT_RS]
-    float* mix = raw + (size_t)H * TT_ROWS * TT_RS;        // [H][H]
+    // This block's heads and kv heads: all of them, or its share of the cluster's.
+    const int rank = CL > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int HL = H / CL, GL = G / CL, h_first = rank * HL, g_first = rank * GL;
+    const int plane = GL * HEAD_BYTES;                     // a tile's keys of this block's kv heads; their values follow
+    float* raw = reinterpret_cast<float*>(tt_smem + (size_t)stages * 2 * plane);      // [H][16][TT_RS]: all heads' raw scores
+    float* mix = raw + (size_t)H * TT_ROWS * TT_RS;        // [HL][H]: the rows of the mix that make this block's heads
+    float* raw_of[CL];                                     // every block's copy of the raw scores, as this block writes them
+#pragma unroll
+    for (int c = 0; c < CL; c++) raw_of[c] = CL > 1 ? cg::this_cluster().map_shared_rank(raw, c) : raw;
+    auto sync_heads = [&]() {                              // all heads' warps: the block's, or the cluster's
+        if (CL > 1) cg::this_cluster().sync();
+        else __syncthreads();
+    };
 
     pdl_launch_dependents_if_resident();
     pdl_wait();
@@ -253,15 +272,15 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     const int slot = seq_slot[sq];
     const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
     const int n_tiles_q = (n_new + TT_ROWS - 1) / TT_ROWS;
-    const int q_tile = n_tiles_q - 1 - (int)blockIdx.x;    // the last rows see the most: they go first
-    if (slot < 0 || q_tile < 0) return;
+    const int q_tile = n_tiles_q - 1 - (int)blockIdx.x / CL;    // the last rows see the most: they go first
+    if (slot < 0 || q_tile < 0) return;                    // (the same for every block of a cluster)
     const int start = seq_start[sq];
     const int tok0 = q_tile * TT_ROWS, tok_end = min(n_new, tok0 + TT_ROWS);
     const int* pages = page_table + (size_t)slot * max_pages;
     const int group = H / G;
     const int last_pos = start + n_new - 1;                // the last position the sequence holds after this step
 
-    for (int i = threadIdx.x; i < H * H; i += blockDim.x) mix[i] = talk[i];
+    for (int i = threadIdx.x; i < HL * H; i += blockDim.x) mix[i] = talk[(size_t)h_first * H + i];
     auto first_seen = [&](int p) { return window > 0 && p + 1 > window ? p + 1 - window : 0; };
     int pos[2], lo[2];
     bool live[2];
@@ -277,8 +296,13 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     int kept = (min(keep_first, first_seen(p_last)) + TT_KEYS - 1) / TT_KEYS;
     const int win_begin = first_seen(p_first) / TT_KEYS, win_end = p_last / TT_KEYS;
     if (kept >= win_begin) kept = win_begin;
-    const int n_tiles = kept + (win_end - win_begin + 1);
-    auto tile_at = [&](int k) { return k < kept ? k : win_begin + (k - kept); };
+    const int all_tiles = kept + (win_end - win_begin + 1);
+    // With several splits (few rows a sequence: single rows above all) block z walks its share of the tiles and leaves its
+    // maxima, sums and products in scratch memory for the merge.
+    const int per_split = (all_tiles + splits - 1) / splits;
+    const int tile_first = (int)blockIdx.z * per_split;
+    const int n_tiles = max(0, min(all_tiles, tile_first + per_split) - tile_first);
+    auto tile_at = [&](int k) { k += tile_first; return k < kept ? k : win_begin + (k - kept); };
     auto page_of = [&](int tile) {
         const int pi = tile / 2;
         const int page = pi < max_pages ? pages[pi] : -1;
@@ -289,9 +313,9 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
         if (page < 0) return;
         const uint32_t kb = ad_smem(tt_smem + (size_t)stage * 2 * plane), vb = kb + plane;
         const int per_head = TT_KEYS * CHUNKS;
-        for (int i = threadIdx.x; i < G * per_head; i += blockDim.x) {
+        for (int i = threadIdx.x; i < GL * per_head; i += blockDim.x) {
             const int g = i / per_head, rest = i - g * per_head, row = rest / CHUNKS, c = rest - row * CHUNKS;
-            const size_t src = (((size_t)page * G + g) * BC_PAGE + (tile & 1) * TT_KEYS + row) * D + c * 8;
+            const size_t src = (((size_t)page * G + g_first + g) * BC_PAGE + (tile & 1) * TT_KEYS + row) * D + c * 8;
             cp_async16(kb + g * HEAD_BYTES + tile_offset<D>(row, c), k_cache + src);
             cp_async16(vb + g * HEAD_BYTES + tile_offset<D>(row, c), v_cache + src);
         }
@@ -302,14 +326,14 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     float o[HPW][ND][4], m[HPW][2], l[HPW][2], factor[HPW];
 #pragma unroll
     for (int a = 0; a < HPW; a++) {
-        const int h = warp + a * warps;
-        factor[a] = h < H ? scale * temp[h] : 0.0f;
+        const int hl = warp + a * warps, h = h_first + hl;      // the head's number in this block, and in the model
+        factor[a] = hl < HL ? scale * temp[h] : 0.0f;
 #pragma unroll
         for (int kd = 0; kd < KD; kd++)
 #pragma unroll
             for (int i = 0; i < 2; i++) {
-                const bf16* qr = q + ((size_t)(row0 + tok0 + gq + 8 * i) * H + (h < H ? h : 0)) * D + kd * 16 + 2 * tq;
-                const bool ok = live[i] && h < H;
+                const bf16* qr = q + ((size_t)(row0 + tok0 + gq + 8 * i) * H + (hl < HL ? h : 0)) * D + kd * 16 + 2 * tq;
+                const bool ok = live[i] && hl < HL;
                 qf[a][kd][i] = ok ? *reinterpret_cast<const uint32_t*>(qr) : 0u;
                 qf[a][kd][i + 2] = ok ? *reinterpret_cast<const uint32_t*>(qr + 8) : 0u;
             }
@@ -331,7 +355,7 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
             cp_async_commit();
         }
         cp_async_wait<0>();
-        __syncthreads();
+        sync_heads();                                      // the tile has come, and nobody reads the raw scores of the tile before any more (so they may be overwritten, from any block)
         if (stages > 1 && it + 1 < n_tiles) load_tile(tile_at(it + 1), stage ^ 1);
         cp_async_commit();
         const int tile = tile_at(it);
@@ -341,7 +365,7 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
             // What lies past the sequence's last position belongs to nobody (a sequence that held the page before may have left
             // not-a-numbers there, and 0 x NaN is NaN in the product with the values): those value rows are cleared in the copy.
             const int first = last_pos % TT_KEYS + 1;
-            for (int i = threadIdx.x; i < G * (TT_KEYS - first) * CHUNKS; i += blockDim.x) {
+            for (int i = threadIdx.x; i < GL * (TT_KEYS - first) * CHUNKS; i += blockDim.x) {
                 const int g = i / ((TT_KEYS - first) * CHUNKS), rest = i - g * (TT_KEYS - first) * CHUNKS;
                 *reinterpret_cast<uint4*>(tt_smem + (size_t)stage * 2 * plane + plane + g * HEAD_BYTES + tile_offset<D>(first + rest / CHUNKS, rest % CHUNKS)) =
                     make_uint4(0u, 0u, 0u, 0u);
@@ -351,9 +375,9 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
         // 1. raw scores of this warp's heads
 #pragma unroll
         for (int a = 0; a < HPW; a++) {
-            const int h = warp + a * warps;
-            if (h >= H) continue;
-            const uint32_t kh = kb + (h / group) * HEAD_BYTES;
+            const int hl = warp + a * warps, h = h_first + hl;
+            if (hl >= HL) continue;
+            const uint32_t kh = kb + (h / group - g_first) * HEAD_BYTES;
             float s[4][4];
 #pragma unroll
             for (int nb = 0; nb < 4; nb++) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
@@ -366,26 +390,28 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
                     mma_16816(s[2 * np], qf[a][kd], b0, b1);
                     mma_16816(s[2 * np + 1], qf[a][kd], b2, b3);
                 }
-            float* rh = raw + (size_t)h * TT_ROWS * TT_RS;
 #pragma unroll
             for (int nb = 0; nb < 4; nb++)
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                     float v0 = s[nb][2 * i] * factor[a], v1 = s[nb][2 * i + 1] * factor[a];
                     if (cap > 0.0f) v0 = tt_bound(v0, cap, two_over_cap), v1 = tt_bound(v1, cap, two_over_cap);
-                    *reinterpret_cast<float2*>(rh + (gq + 8 * i) * TT_RS + nb * 8 + 2 * tq) = make_float2(v0, v1);
+#pragma unroll
+                    for (int c = 0; c < CL; c++)
+                        *reinterpret_cast<float2*>(raw_of[c] + (size_t)h * TT_ROWS * TT_RS + (gq + 8 * i) * TT_RS + nb * 8 + 2 * tq) = make_float2(v0, v1);
                 }
         }
-        __syncthreads();
+        sync_heads();
         // 2. this warp's heads: the mix of all heads' raw scores, the softmax's step, the product with the values
 #pragma unroll
         for (int a = 0; a < HPW; a++) {
-            const int h = warp + a * warps;
-            if (h >= H) continue;
+            const int hl = warp + a * warps, h = h_first + hl;
+            if (hl >= HL) continue;
             float s[4][4];
 #pragma unroll
             for (int nb = 0; nb < 4; nb++) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
-            const float* mh = mix + (size_t)h * H;
+            const float* mh = mix + (size_t)hl * H;
+#pragma unroll 4
             for (int mm = 0; mm < H; mm++) {
                 const float f = mh[mm];
                 const float* rm = raw + (size_t)mm * TT_ROWS * TT_RS;
@@ -433,7 +459,7 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
             for (int nd = 0; nd < ND; nd++) {
                 o[a][nd][0] *= corr[0]; o[a][nd][1] *= corr[0]; o[a][nd][2] *= corr[1]; o[a][nd][3] *= corr[1];
             }
-            const uint32_t vh = vb + (h / group) * HEAD_BYTES;
+            const uint32_t vh = vb + (h / group - g_first) * HEAD_BYTES;
 #pragma unroll
             for (int kk = 0; kk < 2; kk++) {
                 const uint32_t pf[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
@@ -449,16 +475,24 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
         }
     }
     cp_async_wait<0>();
+    if (CL > 1) cg::this_cluster().sync();                 // no block leaves while another may still write raw scores into its memory
 #pragma unroll
     for (int a = 0; a < HPW; a++) {
-        const int h = warp + a * warps;
-        if (h >= H) continue;
+        const int hl = warp + a * warps, h = h_first + hl;
+        if (hl >= HL) continue;
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             float sum = l[a][i];
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             if (!live[i]) continue;
+            if (splits > 1) {
+                float* part = scratch + (((size_t)(row0 + tok0 + gq + 8 * i) * H + h) * splits + blockIdx.z) * (D + 2);
+                if (tq == 0) part[0] = m[a][i], part[1] = sum;
+#pragma unroll
+                for (int nd = 0; nd < ND; nd++) *reinterpret_cast<float2*>(part + 2 + nd * 8 + 2 * tq) = make_float2(o[a][nd][2 * i], o[a][nd][2 * i + 1]);
+                continue;
+            }
             const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
             const size_t at = ((size_t)(row0 + tok0 + gq + 8 * i) * H + h) * D + 2 * tq;
 #pragma unroll
@@ -470,62 +504,135 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     }
 }
 
-static size_t tt_smem_bytes(int H, int G, int D, int stages) {
-    return (size_t)stages * 2 * G * TT_KEYS * D * 2 + ((size_t)H * TT_ROWS * TT_RS + (size_t)H * H) * sizeof(float);
+// One block a (row, head): the splits' maxima (in powers of two), sums and products in the order of the splits, then the gate.
+__global__ void __launch_bounds__(128)
+talk_merge_kernel(const float* scratch, const int* __restrict__ row_slot, const float* gate, bf16* __restrict__ out, int H, int D, int splits) {
+    __shared__ float wz[64];
+    pdl_launch_dependents_if_resident();
+    pdl_wait();
+    PDL_FRESH(scratch); PDL_FRESH(gate);
+    const int r = blockIdx.x, h = blockIdx.y;
+    const size_t at = ((size_t)r * H + h) * D;
+    if (row_slot[r] < 0) {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) out[at + d] = __float2bfloat16_rn(0.0f);
+        return;
+    }
+    const float* part = scratch + ((size_t)r * H + h) * splits * (D + 2);
+    float top = -INFINITY;
+    for (int z = 0; z < splits; z++) top = fmaxf(top, part[(size_t)z * (D + 2)]);
+    if (threadIdx.x < splits) {
+        const float mz = part[(size_t)threadIdx.x * (D + 2)];
+        wz[threadIdx.x] = mz == -INFINITY ? 0.0f : fast_exp2(mz - top);
+    }
+    __syncthreads();
+    float total = 0.0f;
+    for (int z = 0; z < splits; z++) total += wz[z] * part[(size_t)z * (D + 2) + 1];
+    const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int z = 0; z < splits; z++) {
+            const float w = wz[z];
+            if (w > 0.0f) acc = fmaf(w, part[(size_t)z * (D + 2) + 2 + d], acc);      // a split that saw nothing may hold anything
+        }
+        out[at + d] = __float2bfloat16_rn(acc * inv * gate[at + d]);
+    }
 }
-// Heads a warp takes: one up to sixteen heads, two up to thirty-two; a warp's accumulators hold HPW * D value columns.
-static int tt_heads_per_warp(int H) { return H <= 16 ? 1 : 2; }
+
+extern "C" long long bc_talk_tiles_scratch_floats(int rows, int H, int D, int splits) {
+    return splits <= 1 ? 0 : (long long)rows * H * splits * (D + 2);
+}
+
+// Shared memory of one block that owns H / CL heads and G / CL kv heads.
+static size_t tt_smem_bytes(int H, int G, int D, int stages, int CL) {
+    return (size_t)stages * 2 * (G / CL) * TT_KEYS * D * 2 + ((size_t)H * TT_ROWS * TT_RS + (size_t)(H / CL) * H) * sizeof(float);
+}
+// How the heads are shared out: (blocks a cluster, heads a warp), or (0, 0) where the tiles do not take these sizes.  One block of
+// up to sixteen warps, a head each; more heads as a cluster of two or four such blocks, where heads and kv heads divide evenly;
+// else two heads a warp in one block, whose accumulators then hold 2 D value columns a thread (D up to 64).
+static void tt_shape(int H, int G, int D, int* CL, int* HPW) {
+    *CL = *HPW = 0;
+    if (H <= 0 || G <= 0 || H % G || D % 16 || D < 16 || D > 128) return;
+    if (H <= 16) { *CL = 1, *HPW = 1; return; }
+    for (int c = 2; c <= 4; c *= 2)
+        if (H <= 16 * c && H % c == 0 && G % c == 0) { *CL = c, *HPW = 1; return; }
+    if (H <= 32 && D <= 64) *CL = 1, *HPW = 2;
+}
 
 extern "C" int bc_talk_tiles_accepts(int H, int G, int D) {
-    if (H <= 0 || G <= 0 || H % G || H > 32 || D % 16 || D < 16 || D > 128 || tt_heads_per_warp(H) * D > 128) return 0;
-    return tt_smem_bytes(H, G, D, 1) <= 200 * 1024;
+    int CL, HPW;
+    tt_shape(H, G, D, &CL, &HPW);
+    return CL > 0 && tt_smem_bytes(H, G, D, 1, CL) <= 216 * 1024;
 }
 
-template <int D, int HPW>
+template <int D, int HPW, int CL>
 static int tiles_go(const void* q, const void* k_cache, const void* v_cache, const int* page_table, const int* seq_rows, const int* seq_slot,
                     const int* seq_start, const float* gate, const float* temp, const float* talk, void* out, int seqs, int max_new, int H, int G,
-                    int max_pages, int n_pages, int window, int keep_first, float scale, float cap, cudaStream_t s) {
-    const int stages = tt_smem_bytes(H, G, D, 2) <= 200 * 1024 ? 2 : 1;
-    const size_t smem = tt_smem_bytes(H, G, D, stages);
+                    int max_pages, int n_pages, int window, int keep_first, float scale, float cap, float* scratch, int splits, const int* row_slot,
+                    int rows, cudaStream_t s) {
+    const int stages = tt_smem_bytes(H, G, D, 2, CL) <= 216 * 1024 ? 2 : 1;
+    const size_t smem = tt_smem_bytes(H, G, D, stages, CL);
     static size_t configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(talk_tiles_kernel<D, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(talk_tiles_kernel<D, HPW, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             bc_set_error("talk_tiles: cannot set shared memory to %zu: %s", smem, cudaGetErrorString(e));
             return (int)e;
         }
         configured = smem;
     }
-    const int warps = (H + HPW - 1) / HPW;
-    bc_launch(talk_tiles_kernel<D, HPW>, dim3((max_new + TT_ROWS - 1) / TT_ROWS, seqs), dim3(32 * warps), smem, s, (const bf16*)q, (const bf16*)k_cache,
-              (const bf16*)v_cache, page_table, seq_rows, seq_slot, seq_start, gate, temp, talk, (bf16*)out, H, G, max_pages, n_pages, window, keep_first,
-              scale, cap, stages);
+    const int warps = (H / CL + HPW - 1) / HPW;
+    const dim3 grid(((max_new + TT_ROWS - 1) / TT_ROWS) * CL, seqs, splits);
+    cudaError_t e;
+    if (CL > 1)
+        e = bc_launch_clustered(talk_tiles_kernel<D, HPW, CL>, grid, dim3(32 * warps), smem, s, dim3(CL, 1, 1), (const bf16*)q, (const bf16*)k_cache,
+                                (const bf16*)v_cache, page_table, seq_rows, seq_slot, seq_start, gate, temp, talk, (bf16*)out, H, G, max_pages, n_pages,
+                                window, keep_first, scale, cap, stages, scratch, splits);
+    else
+        e = bc_launch(talk_tiles_kernel<D, HPW, CL>, grid, dim3(32 * warps), smem, s, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                      page_table, seq_rows, seq_slot, seq_start, gate, temp, talk, (bf16*)out, H, G, max_pages, n_pages, window, keep_first, scale, cap,
+                      stages, scratch, splits);
+    if (e != cudaSuccess) {
+        bc_set_error("talk_tiles: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    if (splits > 1) bc_launch(talk_merge_kernel, dim3(rows, H), dim3(128), 0, s, (const float*)scratch, row_slot, gate, (bf16*)out, H, D, splits);
     BC_LAUNCH_STATUS();
 }
 
 // q: [rows, H D] bf16; k_cache, v_cache: [pages, G, BC_PAGE, D] bf16; gate: [rows, H D] float; temp: [H]; talk: [H, H]; out: [rows, H D] bf16.
-// Sequence s brings rows seq_rows[s] .. seq_rows[s + 1] and held seq_start[s] positions before.
+// Sequence s brings rows seq_rows[s] .. seq_rows[s + 1] and held seq_start[s] positions before.  splits > 1 (few rows a sequence): the
+// tiles of positions a block would walk are shared out over that many blocks, which leave their parts in scratch (floats as
+// bc_talk_tiles_scratch_floats says) for a second kernel; then row_slot [rows] tells which of the `rows` rows of q belong to no sequence.
 extern "C" int bc_talk_tiles_bf16(const void* q, const void* k_cache, const void* v_cache, const int* page_table, const int* seq_rows, const int* seq_slot,
                                   const int* seq_start, const float* gate, const float* temp, const float* talk, void* out, int seqs, int max_new, int H,
-                                  int G, int D, int max_pages, int n_pages, int window, int keep_first, float scale, float cap, cudaStream_t s) {
-    BC_CHECK_ARG(bc_talk_tiles_accepts(H, G, D), "talk_tiles: %d heads on %d of %d are not taken (up to 32 heads, heads of multiples of 16 up to 128, "
-                 "up to 64 with more than 16 heads)", H, G, D);
+                                  int G, int D, int max_pages, int n_pages, int window, int keep_first, float scale, float cap, float* scratch, int splits,
+                                  const int* row_slot, int rows, cudaStream_t s) {
+    BC_CHECK_ARG(splits >= 1 && splits <= 64 && (splits == 1 || (scratch && row_slot && rows >= 0)), "talk_tiles: %d splits (1 to 64) or their scratch", splits);
+    BC_CHECK_ARG(bc_talk_tiles_accepts(H, G, D), "talk_tiles: %d heads on %d of %d are not taken (heads of multiples of 16 up to 128; up to 16 heads, "
+                 "or up to 64 where a cluster of two or four blocks shares heads and kv heads out evenly)", H, G, D);
     BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && window >= 0 && keep_first >= 0 && cap >= 0.0f && temp && talk && gate,
                  "talk_tiles: bad sizes seqs=%d max_new=%d window=%d kept=%d", seqs, max_new, window, keep_first);
     if (seqs == 0 || max_new == 0) return BC_OK;
-#define TT_GO(DD, HH) return tiles_go<DD, HH>(q, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, gate, temp, talk, out, seqs, max_new, H, G, \
-                                              max_pages, n_pages, window, keep_first, scale, cap, s)
-    const int hpw = tt_heads_per_warp(H);
-    switch (D) {
-        case 16: if (hpw == 1) TT_GO(16, 1); TT_GO(16, 2);
-        case 32: if (hpw == 1) TT_GO(32, 1); TT_GO(32, 2);
-        case 48: if (hpw == 1) TT_GO(48, 1); TT_GO(48, 2);
-        case 64: if (hpw == 1) TT_GO(64, 1); TT_GO(64, 2);
-        case 80: TT_GO(80, 1);
-        case 96: TT_GO(96, 1);
-        case 112: TT_GO(112, 1);
-        case 128: TT_GO(128, 1);
+    int CL, HPW;
+    tt_shape(H, G, D, &CL, &HPW);
+#define TT_GO(DD, HH, CC) return tiles_go<DD, HH, CC>(q, k_cache, v_cache, page_table, seq_rows, seq_slot, seq_start, gate, temp, talk, out, seqs, max_new, H, \
+                                                      G, max_pages, n_pages, window, keep_first, scale, cap, scratch, splits, row_slot, rows, s)
+#define TT_D(DD)                         \
+    case DD:                             \
+        if (CL == 2) TT_GO(DD, 1, 2);    \
+        if (CL == 4) TT_GO(DD, 1, 4);    \
+        if (HPW == 1) TT_GO(DD, 1, 1);   \
+        break;
+    if (HPW == 2) {
+        switch (D) {
+            case 16: TT_GO(16, 2, 1);
+            case 32: TT_GO(32, 2, 1);
+            case 48: TT_GO(48, 2, 1);
+            case 64: TT_GO(64, 2, 1);
+        }
     }
+    switch (D) { TT_D(16) TT_D(32) TT_D(48) TT_D(64) TT_D(80) TT_D(96) TT_D(112) TT_D(128) }
+#undef TT_D
 #undef TT_GO
     bc_set_error("talk_tiles: heads of %d are not taken", D);
     return BC_ERR_ARG;

@@ -256,4 +256,14 @@ __host__ __device__ constexpr uint32_t instr_desc(int n) { return (1u << 4) | (1
 // The gate of the bf16 path: hardware exponential and division (errors of a few float ulp,
 // far below the bf16 rounding that follows).
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+// The gate with bounds, where `limit` is positive: g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1);
+// else the plain gate above.  The choice is the launch's, the same for every thread.
+__device__ __forceinline__ float glu_mul(float g, float u, float limit, float alpha) {
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+        return __fdividef(g, 1.0f + __expf(-alpha * g)) * u;
+    }
+    return silu_mul(g, u);
+}
 

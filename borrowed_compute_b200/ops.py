@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -159,7 +159,7 @@ _CLASS_OF = {
     "bc_latent_prepare": "latent norm + append", "bc_latent_query": "latent query", "bc_latent_rows": "attention", "bc_latent_decode": "attention", "bc_latent_heads": "latent query",
     "bc_latent_gather": "latent keys and values", "bc_latent_spread": "latent keys and values", "bc_latent_gate": "latent values",
     "bc_latent_values": "latent values", "bc_norm_add": "norm", "bc_relu2": "activation", "bc_glu_clipped": "activation",
-    "bc_talk_prepare": "rotary + append", "bc_talk_rows": "attention", "bc_talk_tiles": "attention", "bc_scale": "softcap", "bc_add_bias": "bias", "bc_gated_add": "gated sum", "bc_moe_table_route": "routing",
+    "bc_talk_prepare": "talk prepare", "bc_talk_rows": "talking attention", "bc_talk_tiles": "talking attention", "bc_scale": "softcap", "bc_add_bias": "bias", "bc_gated_add": "gated sum", "bc_moe_table_route": "routing",
 }
 
 
@@ -364,10 +364,12 @@ def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     return max(1, min(sms // tiles, -(-K // 64) // 8, 16, fits))
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, splits: Optional[int] = None) -> None:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, splits: Optional[int] = None,
+            glu: Optional[Tuple[float, float]] = None) -> None:
     """out = x @ w.T for bf16 operands on the tcgen05 tensor cores (float accumulation in
     TMEM), with the epilogues of gemm_simt.  ``splits`` > 1 cuts K across blocks that add
-    their partial sums in a fixed order."""
+    their partial sums in a fixed order.  ``glu`` = (limit, alpha) turns EPI_SWIGLU's gate into the bounded one:
+    out = g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)."""
     _need(x, "x", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     M, K = x.shape
@@ -389,6 +391,13 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
         accs = 2 if epilogue == EPI_SWIGLU else 1
         if tiles * splits * accs * rows * bn > partial.numel() or tiles * 4 > counters.numel():
             raise KernelError(f"gemm_tc: {tiles} tiles are too many for the split-K scratch; use splits=1")
+    if glu is not None:
+        # The gated product with bounds (limit, alpha): out = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
+        if epilogue != EPI_SWIGLU:
+            raise KernelError("gemm_tc: bounds come with the gated product (EPI_SWIGLU)")
+        _call(_fn("bc_gemm_tc_glu_bf16"), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(splits), _ptr(partial), _ptr(counters),
+              _c_float(glu[0]), _c_float(glu[1]), _stream())
+        return
     _call(_fn("bc_gemm_tc_bf16"), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue), _c_int(splits),
           _ptr(partial), _ptr(counters), _stream())
 
@@ -974,10 +983,12 @@ def talk_tiles_accepts(heads: int, kv_heads: int, head_dim: int, dtype: torch.dt
 
 def talk_tiles(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, seq_rows: torch.Tensor, seq_slot: torch.Tensor,
                seq_start: torch.Tensor, gate: torch.Tensor, temp: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
-               heads: int, kv_heads: int, head_dim: int, window: int, keep_first: int, scale: float, cap: float) -> None:
-    """What talk_rows computes, for bf16 prompts on mma.sync tiles: a block owns sixteen rows of one sequence and all heads, so that
+               heads: int, kv_heads: int, head_dim: int, window: int, keep_first: int, scale: float, cap: float, splits: int = 1,
+               row_slot: Optional[torch.Tensor] = None) -> None:
+    """What talk_rows computes, for bf16 on mma.sync tiles: a block owns sixteen rows of one sequence and all heads, so that
     every head can mix its score out of all heads' raw scores; sequence s brings rows seq_rows[s] .. seq_rows[s + 1] and held
-    seq_start[s] positions before."""
+    seq_start[s] positions before.  ``splits`` > 1 (steps of few rows a sequence) shares the positions a block would walk out over
+    that many blocks and merges their parts in a second kernel, in the order of the splits; ``row_slot`` then marks padding rows."""
     _talk_check("talk_tiles", q, k_cache, v_cache, gate, temp, talk, out, heads, kv_heads, head_dim)
     _need(q, "q", torch.bfloat16)
     for t, name in ((page_table, "page_table"), (seq_rows, "seq_rows"), (seq_slot, "seq_slot"), (seq_start, "seq_start")):
@@ -987,9 +998,25 @@ def talk_tiles(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pa
     _bounds("talk_tiles: seq_slot", seq_slot, page_table.shape[0], seqs, lowest=-1)
     _bounds("talk_tiles: seq_rows", seq_rows, out.shape[0] + 1, seqs + 1)
     _bounds("talk_tiles: page_table", page_table, k_cache.shape[0], lowest=-1)
+    scratch = None
+    if splits > 1:
+        _need(row_slot, "row_slot", torch.int32)
+        scratch, _ = _decode_workspace(q.device, q.shape[0] * heads * splits * (head_dim + 2), 1)
     _call(_fn("bc_talk_tiles_bf16"), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows), _ptr(seq_slot), _ptr(seq_start), _ptr(gate),
           _ptr(temp), _ptr(talk), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_table.shape[1]),
-          _c_int(k_cache.shape[0]), _c_int(window), _c_int(keep_first), _c_float(scale), _c_float(cap), _stream())
+          _c_int(k_cache.shape[0]), _c_int(window), _c_int(keep_first), _c_float(scale), _c_float(cap), _ptr(scratch), _c_int(splits),
+          _ptr(row_slot if splits > 1 else None), _c_int(q.shape[0]), _stream())
+
+
+def talk_tiles_splits(seqs: int, heads: int, reach: int, window: int, keep_first: int) -> int:
+    """Splits of the positions a row sees (tiles of 32) for steps of few rows a sequence, so that the blocks fill the machine ONCE (a
+    block takes most of a multiprocessor's shared memory, and more than sixteen heads take two or four blocks a sequence): never
+    more than there are tiles (``reach``: a bound on the positions any row reaches; a window bounds them further)."""
+    tiles = -(-max(reach, 1) // 32)
+    if window > 0:
+        tiles = min(tiles, -(-keep_first // 32) + (window + 30) // 32 + 1)
+    blocks = max(seqs, 1) * (1 if heads <= 16 else 2 if heads <= 32 else 4)
+    return max(1, min(tiles, sm_count() // blocks, 64))
 
 
 # ------------------------------------------------------------------------------ routed experts

@@ -73,7 +73,10 @@ class PlainMLP(FeedForward):
 class ClippedGLU(FeedForward):
     """down( g sigmoid(alpha g) (u + 1) ) with g = min(gate x, limit) and u = clamp(up x, -limit, limit): a gated feed-forward
     whose gate saturates from above, whose up branch is bounded on both sides and carries a one.  Gate and up are one product
-    with float sums; the activation works on those and rounds once."""
+    with float sums; the activation works on those and rounds once: in the product's epilogue on the tensor cores, in a kernel
+    of its own after the CUDA-core product (the 32-bit path, and the checked twin: ``fused = False``)."""
+
+    fused = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702, gate: str = "gate", up: str = "up",
                  down: str = "down"):
@@ -96,8 +99,11 @@ class ClippedGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         rows, F = x.shape[0], self.intermediate_size
-        z = torch.empty((rows, 2 * F), dtype=torch.float32, device=x.device)
-        products.linear(x, self.w_gate_up, z, products.EPI_STORE_F32, "gate/up product")
         act = torch.empty((rows, F), dtype=x.dtype, device=x.device)
-        ops.glu_clipped(z, act, self.limit, self.alpha)
+        if self.fused and products.takes_tensor_cores(x, self.w_gate_up):
+            products.linear(x, self.w_gate_up, act, products.EPI_SWIGLU, "gate/up product", glu=(self.limit, self.alpha))
+        else:
+            z = torch.empty((rows, 2 * F), dtype=torch.float32, device=x.device)
+            products.linear(x, self.w_gate_up, z, products.EPI_STORE_F32, "gate/up product")
+            ops.glu_clipped(z, act, self.limit, self.alpha)
         products.linear(act, self.w_down, residual, products.EPI_ADD_F32, "down product")

@@ -16,16 +16,24 @@ from ..ops import EPI_ADD_F32, EPI_RELU2, EPI_STORE, EPI_STORE_F32, EPI_SWIGLU  
 force_simt = False
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, what: str = "") -> None:
-    """``what`` names the product for a profile of the step ("qkv", "head", ...)."""
+def takes_tensor_cores(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``linear`` multiplies these operands on the tensor cores."""
+    return x.dtype == torch.bfloat16 and not force_simt and hasattr(ops, "gemm_tc") and ops.gemm_tc_accepts(x, w)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, what: str = "", glu=None) -> None:
+    """``what`` names the product for a profile of the step ("qkv", "head", ...).  ``glu`` = (limit, alpha): the bounded gate of
+    the tensor-core product's gated epilogue (callers ask ``takes_tensor_cores`` first)."""
     if ops.timeline is not None and what:
         ops.label = what
         try:
-            linear(x, w, out, epilogue)
+            linear(x, w, out, epilogue, glu=glu)
         finally:
             ops.label = ""
         return
-    if x.dtype == torch.bfloat16 and not force_simt and hasattr(ops, "gemm_tc") and ops.gemm_tc_accepts(x, w):
-        ops.gemm_tc(x, w, out, epilogue)
+    if takes_tensor_cores(x, w):
+        ops.gemm_tc(x, w, out, epilogue, glu=glu)
+    elif glu is not None:
+        raise ops.KernelError("a bounded gate in the epilogue comes with the tensor-core product")
     else:
         ops.gemm_simt(x, w, out, epilogue)

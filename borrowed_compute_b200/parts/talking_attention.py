@@ -26,7 +26,7 @@ from . import products
 from .base import MIXERS, POSITION_ENCODINGS, CacheNeed, Mixer, RunMemory, Runtime, StepContext, TensorSpec
 
 
-# Tests: "rows" (one block a row: the checked twin) or "tiles" (tensor-core tiles for prompts) wherever the sizes allow it;
+# Tests: "rows" (one block a row: the checked twin) or "tiles" (tensor-core tiles, bfloat16) wherever the sizes allow it;
 # None: the part chooses.
 force: Optional[str] = None
 
@@ -81,7 +81,7 @@ class TalkingAttention(Mixer):
         tiles = ops.talk_tiles_accepts(self.heads, self.kv_heads, self.head_dim, dtype)
         if force == "rows" or (force == "tiles" and tiles):
             return force
-        return "tiles" if tiles and not ctx.decode and ctx.max_new > 1 else "rows"
+        return "tiles" if tiles else "rows"
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
         rows, dev = x.shape[0], x.device
@@ -98,8 +98,11 @@ class TalkingAttention(Mixer):
                          write_cache=mem.writes)
         att = torch.empty((rows, H * D), dtype=x.dtype, device=dev)
         if self.path(ctx, x.dtype) == "tiles":
+            # Few rows a sequence (single rows above all) leave few blocks: the positions are then shared out over several.
+            splits = ops.talk_tiles_splits(ctx.seqs, H, ctx.max_total, self.window, self.keep_first) if ctx.max_new <= 16 else 1
             ops.talk_tiles(q, mem.k_pages, mem.v_pages, mem.page_table, ctx.seq_rows, ctx.seq_slot, ctx.seq_start, gate, self.temp, self.talk, att,
-                           ctx.seqs, ctx.max_new, H, G, D, self.window, self.keep_first, self.scale, self.softcap)
+                           ctx.seqs, ctx.max_new, H, G, D, self.window, self.keep_first, self.scale, self.softcap, splits=splits,
+                           row_slot=ctx.row_slot)
         else:
             ops.talk_rows(q, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, gate, self.temp, self.talk, att, H, G, D,
                           self.window, self.keep_first, self.scale, self.softcap)

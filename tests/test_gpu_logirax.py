@@ -184,7 +184,7 @@ def test_token_shift_keeps_the_last_input_of_every_sequence(dtype, E):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("E,F,limit,rows", [(16, 24, 1.0, 5), (40, 52, 0.25, 70), (64, 128, 7.0, 300)])
+@pytest.mark.parametrize("E,F,limit,rows", [(16, 24, 1.0, 5), (40, 52, 0.25, 70), (64, 128, 7.0, 300), (512, 1024, 1.0, 9), (256, 384, 2.0, 700)])
 def test_feed_forward_with_a_clipped_gate(dtype, E, F, limit, rows):
     """Inputs large enough that the gate meets its bound from above and the up branch both of its bounds."""
     from borrowed_compute_b200.parts import FEED_FORWARDS
@@ -197,9 +197,11 @@ def test_feed_forward_with_a_clipped_gate(dtype, E, F, limit, rows):
     assert (g > limit).any() and (u > limit).any() and (u < -limit).any() and (np.abs(g) < limit).any()
     part = FEED_FORWARDS.get("clipped_glu")(hidden_size=E, intermediate_size=F, limit=limit)
     rt = load_part(part, w, torch_type(dtype))
-    out = torch.zeros((rows, E), dtype=torch.float32, device=DEV)
-    part.forward(dev(x, rt.dtype), out, None)
-    close(out.cpu().numpy(), pl.clipped_glu(x, {"limit": limit}, w, ""), dtype)
+    for fused in (True, False):          # in the tensor-core product's epilogue, and in the kernel of its own
+        part.fused = fused
+        out = torch.zeros((rows, E), dtype=torch.float32, device=DEV)
+        part.forward(dev(x, rt.dtype), out, None)
+        close(out.cpu().numpy(), pl.clipped_glu(x, {"limit": limit}, w, ""), dtype, f"fused {fused}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -325,9 +327,11 @@ def test_talking_attention_with_one_key_that_matters_at_every_edge(dtype, path, 
 
 @pytest.mark.parametrize("dtype,path", TALK_PATHS)
 @pytest.mark.parametrize("H,G,D,rot,window,keep,cap", [(1, 1, 8, 8, 0, 0, 0.0), (6, 2, 40, 20, 100, 5, 10.0), (40, 8, 16, 0, 50, 1, 50.0), (3, 3, 128, 64, 64, 64, 0.0),
-                                                       (16, 4, 64, 32, 77, 0, 20.0), (5, 1, 12, 4, 300, 7, 3.0), (8, 8, 48, 48, 31, 2, 25.0)])
+                                                       (16, 4, 64, 32, 77, 0, 20.0), (5, 1, 12, 4, 300, 7, 3.0), (8, 8, 48, 48, 31, 2, 25.0),
+                                                       (32, 8, 128, 64, 100, 4, 30.0), (24, 6, 32, 16, 40, 0, 0.0), (20, 5, 64, 64, 90, 33, 12.0)])
 def test_talking_attention_in_other_sizes(dtype, path, H, G, D, rot, window, keep, cap):
-    """One head; more heads than warps of a block; heads that are no power of two; every dimension turning, or none; no window."""
+    """One head; more heads than a block takes (two and four blocks a cluster share them out, or two heads a warp where the kv heads
+    do not divide); heads that are no power of two; every dimension turning, or none; no window."""
     from borrowed_compute_b200 import StepEntry
     from borrowed_compute_b200.parts import talking_attention
 
