@@ -160,7 +160,7 @@ def test_norm_with_a_weight_stored_around_zero(dtype, E):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("E", [8, 36, 256])
+@pytest.mark.parametrize("E", [8, 36, 264])
 def test_token_shift_keeps_the_last_input_of_every_sequence(dtype, E):
     """Portions of many sizes and single rows continue where the sequence stopped; a slot handed out anew starts from zeros."""
     from borrowed_compute_b200 import StepEntry
@@ -184,7 +184,7 @@ def test_token_shift_keeps_the_last_input_of_every_sequence(dtype, E):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("E,F,limit,rows", [(16, 24, 1.0, 5), (40, 52, 0.25, 70), (64, 128, 7.0, 300), (512, 1024, 1.0, 9), (256, 384, 2.0, 700)])
+@pytest.mark.parametrize("E,F,limit,rows", [(16, 24, 1.0, 5), (40, 52, 0.25, 70), (64, 128, 7.0, 300), (512, 1024, 1.5, 9), (264, 384, 2.0, 700)])
 def test_feed_forward_with_a_clipped_gate(dtype, E, F, limit, rows):
     """Inputs large enough that the gate meets its bound from above and the up branch both of its bounds."""
     from borrowed_compute_b200.parts import FEED_FORWARDS
@@ -205,7 +205,7 @@ def test_feed_forward_with_a_clipped_gate(dtype, E, F, limit, rows):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("E,n,top,ff,shared,factor,rows", [(32, 6, 2, 16, 8, 1.5, 50), (24, 3, 3, 8, 0, 1.0, 9), (40, 12, 4, 24, 16, 2.5, 200), (16, 1, 1, 8, 8, 0.5, 4)])
+@pytest.mark.parametrize("E,n,top,ff,shared,factor,rows", [(32, 6, 2, 16, 8, 1.5, 50), (24, 3, 3, 8, 0, 1.0, 9), (40, 10, 4, 24, 16, 2.5, 200), (16, 1, 1, 8, 8, 0.5, 4)])
 def test_routed_experts_with_weights_that_add_up_to_a_factor(dtype, E, n, top, ff, shared, factor, rows):
     from borrowed_compute_b200 import StepEntry
     from borrowed_compute_b200.parts import FEED_FORWARDS
