@@ -382,6 +382,53 @@ def test_latent_attention_with_a_sink_and_neighbouring_pairs(dtype, path, H, D, 
         close(run_part(part, rt, x, portions, E), ref, dtype, f"portions {portions}")
 
 
+def planted_latent(rng, m, E, star, T, sink):
+    """Weights and inputs of one latent mixer in which position ``star`` outweighs every other position and the sink: only input
+    channel 0 feeds latent channel 0, and it is zero but at ``star``; every head's plain key reads latent channel 0 along a direction
+    of its own, and every query has that direction, fed by input channel 1 (one everywhere) through query-latent channel 0."""
+    H, D, DV, QR, R, rot = m["heads"], m["dim"], m["vdim"], m["q_rank"], m["kv_rank"], m["rot_dim"]
+    mat = lambda r, c, f=1.0: rng.standard_normal((r, c)) * f / math.sqrt(c)                 # noqa: E731
+    w = {"dq": mat(QR, E), "dq.norm": 1.0 + 0.2 * rng.uniform(-1, 1, QR), "uq": mat(H * (D + rot), QR), "dkv": mat(R + rot, E),
+         "dkv.norm": 1.0 + 0.2 * rng.uniform(-1, 1, R), "uk": mat(H * D, R), "uv": mat(H * DV, R, 2.0), "g": mat(H, E, 2.0), "o": mat(E, H * DV),
+         "sink": np.full(H, sink) + 0.25 * np.arange(H)}
+    w["dkv"][:, 0] = 0.0
+    w["dkv"][0, :] = 0.0
+    w["dkv"][0, 0] = 4.0
+    w["dq"][0, :] = 0.0
+    w["dq"][0, 1] = 3.0
+    for h in range(H):
+        direction = rng.choice([-1.0, 1.0], D) * (3.0 / math.sqrt(D * m["scale"]))
+        w["uq"][h * (D + rot):h * (D + rot) + D, 0] = direction
+        w["uk"][h * D:(h + 1) * D, 0] = direction
+    x = rng.standard_normal((T, E)) * 0.5
+    x[:, 0], x[:, 1] = 0.0, 1.0
+    x[star, 0] = 8.0
+    return {k: pl.to_bf16(v) for k, v in w.items()}, pl.to_bf16(x)
+
+
+@pytest.mark.parametrize("dtype,path", LATENT_PATHS)
+@pytest.mark.parametrize("star,rot,sink", [(0, 8, 2.0), (5, 0, 2.0), (63, 8, -1.0), (64, 16, 4.0), (250, 8, 2.0)])
+def test_latent_attention_with_one_far_key_and_a_sink(dtype, path, star, rot, sink):
+    """Every later row returns the planted position's value, hundreds of positions on, less the sink's share: whole, in portions
+    whose borders fall beside the key and the pages' borders, and row by row."""
+    from borrowed_compute_b200 import StepEntry
+    from borrowed_compute_b200.parts import latent_attention
+
+    E, T = 64, 330
+    m = pl.latent_mixer(3, 16, 24, 24, 40, rot, scale=0.25, base=10000.0)
+    w, x = planted_latent(np.random.default_rng(star * 3 + rot), m, E, star, T, sink)
+    ref = pl.latent_attention(x, m, w, "", 1e-5)
+    lost = pl.latent_attention(np.concatenate([x[:star], 0.0 * x[star:star + 1], x[star + 1:]]), m, w, "", 1e-5)
+    assert np.abs(ref[-1] - lost[-1]).max() > 0.05 * np.abs(ref).max()          # the far key decides the last row
+    part = latent_part(m, E, 1e-5)
+    rt = load_part(part, w, torch_type(dtype))
+    latent_attention.force = path
+    if part.path(context([StepEntry(0, [0] * 20)], [0]), rt.dtype) != path:
+        pytest.skip("these sizes do not take this path")
+    for portions in ([T], [star + 1], [max(star, 1), 2, 2], [2, 61, 3, 62, 2, 9, 64, 100]):
+        close(run_part(part, rt, x, portions, E), ref, dtype, f"portions {portions}")
+
+
 # ------------------------------------------------------------------------- whole models
 
 @pytest.mark.parametrize("dtype", DTYPES)
