@@ -13,9 +13,10 @@
 //
 //   prepare   from the fused projection [q | k | gate] (float): bias, rotation, unit norm, q in the activation type, k and the
 //             unrotated, unnormed k (the values) into the cache's two planes at the row's position, gate = sigmoid (float)
-//   rows      one block a row, one warp a head (two heads a warp past 32 heads): the true 32-bit path, the path of single
-//             rows (a row sees at most window + keep_first positions), and the checked twin of the tile kernel
-//   tiles     bf16 prompts on mma.sync tiles: a block owns sixteen rows of one sequence and all heads
+//   rows      one block a row, one warp a head (two heads a warp past 32 heads): the true 32-bit path, any size, and the
+//             checked twin of the tile kernel
+//   tiles     bf16 on mma.sync tiles: a block (or a cluster of blocks) owns sixteen rows of one sequence and all heads; steps of
+//             few rows a sequence share the positions out over several blocks, whose parts a second kernel merges
 //
 // Scores, the bound, the mix, the softmax's weights and all sums are float.  A row's sums run in an order that its position
 // and the sizes alone fix, so a row gives the same bits in any batch and under any cut of its prompt.

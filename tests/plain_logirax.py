@@ -343,20 +343,20 @@ def make_weights(cfg, seed):
 
 def draw_config(rng):
     """A configuration whose sizes, constants and order of layers are drawn."""
-    E = int(rng.choice([24, 40, 64, 72]))
+    E = int(rng.choice([24, 40, 64, 72, 128]))
     layers = []
     for _ in range(int(rng.integers(2, 5))):
         if rng.random() < 0.5:
-            G = int(rng.choice([1, 2, 3]))
-            H = G * int(rng.choice([1, 2, 3]))
-            d = int(rng.choice([8, 12, 16, 32, 40]))
+            G = int(rng.choice([1, 2, 3, 4, 8]))
+            H = G * int(rng.choice([1, 2, 3, 4]))
+            d = int(rng.choice([8, 12, 16, 32, 40, 64, 128]))
             rot = int(rng.choice([0, d // 2 // 2 * 2, d]))
             m = talking_mixer(H, G, d, int(rng.choice([1, 5, 33, 64, 100])), int(rng.choice([0, 1, 4, 66])), rot,
                               softcap=float(rng.choice([0.0, 5.0, 30.0])), base=float(rng.choice([100.0, 10000.0])))
         else:
             rd = int(rng.choice([0, 4, 8, 16]))
-            m = latent_mixer(int(rng.choice([1, 2, 5])), int(rng.choice([8, 16, 24])), int(rng.choice([8, 16, 40])), int(rng.choice([8, 12, 24])),
-                             int(rng.choice([8, 16, 20, 48])), rd, base=float(rng.choice([50.0, 50000.0])))
+            m = latent_mixer(int(rng.choice([1, 2, 5, 18])), int(rng.choice([8, 16, 24, 48, 64])), int(rng.choice([8, 16, 40, 80])),
+                             int(rng.choice([8, 12, 24, 96])), int(rng.choice([8, 16, 20, 48, 128])), rd, base=float(rng.choice([50.0, 50000.0])))
         kind = rng.random()
         if kind < 0.2:
             f = None

@@ -531,7 +531,7 @@ def test_long_decoding_far_past_the_window(dtype):
     mostly_close(run_cut(eng, toks, [20]), ref, dtype)
 
 
-@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("seed", range(10))
 def test_drawn_configurations(seed):
     """Sizes, constants and the order of layers drawn at random, in float32: whole, in portions, and token by token."""
     rng = np.random.default_rng(1000 + seed)
@@ -544,7 +544,7 @@ def test_drawn_configurations(seed):
     close(run_cut(eng, toks, [2, 66, 30]), ref, "float32", f"portions, {json.dumps(cfg)}")
 
 
-@pytest.mark.parametrize("seed", range(4))
+@pytest.mark.parametrize("seed", range(8))
 def test_drawn_configurations_in_bfloat16(seed):
     rng = np.random.default_rng(2000 + seed)
     cfg = pl.draw_config(rng)
