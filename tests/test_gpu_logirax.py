@@ -556,6 +556,22 @@ def test_drawn_configurations_in_bfloat16(seed):
     mostly_close(run_cut(eng, toks, [2, 66, 30]), ref, "bfloat16", f"portions, {json.dumps(cfg)}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sizes_that_are_multiples_of_nothing(dtype):
+    """A width, heads, latents, feed-forwards and a vocabulary that no vector load and no tile divides."""
+    cfg = pl.model(61, 50, [
+        (pl.talking_mixer(3, 1, 10, 7, 2, 6, softcap=9.0), pl.moe(5, 2, 14, 6, 1.25)),
+        (pl.latent_mixer(3, 6, 10, 10, 12, 2), pl.dense(14, 0.75)),
+        (pl.talking_mixer(5, 5, 18, 50, 0, 18, softcap=0.0), None),
+    ], eps=1e-4, embedding_scale=3.0, logit_scale=1.5)
+    w = pl.make_weights(cfg, 77)
+    eng = engine_for(cfg, w, dtype, max_tokens=1024, max_slots=2, max_seq=512)
+    toks = tokens_for(cfg, w, 130, seed=9)
+    ref = pl.forward(cfg, w, toks)
+    mostly_close(run_whole(eng, toks), ref, dtype, "whole")
+    mostly_close(run_cut(eng, toks, [3, 64, 2, 40]), ref, dtype, "portions")
+
+
 # ------------------------------------------------------------------ the entry points
 
 def folder_for(tmp_path, name, seed):
