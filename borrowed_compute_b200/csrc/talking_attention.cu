@@ -233,7 +233,9 @@ talk_rows_kernel(const T* q, const T* k_cache, const T* v_cache, const int* __re
 // tile are then the cluster's.
 #define TT_KEYS 32
 #define TT_ROWS 16
-#define TT_RS 40            // floats a row of raw scores takes in shared memory: 64-bit reads of a quarter-warp's rows meet no bank twice
+#define TT_RS 36            // floats a row of raw scores takes in shared memory.  A row keeps every thread's eight scores side by side
+                            // ([quarter of the lane][n-block][2]), so that they move sixteen bytes at a time; four floats of
+                            // padding a row let the eight threads of such an access meet no bank twice
 
 __device__ __forceinline__ float tt_bound(float s, float cap, float two_over_cap) {
     // cap * tanh(s / cap) = cap * (1 - 2 / (e^(2 s / cap) + 1))
@@ -394,12 +396,18 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
 #pragma unroll
             for (int nb = 0; nb < 4; nb++)
 #pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    float v0 = s[nb][2 * i] * factor[a], v1 = s[nb][2 * i + 1] * factor[a];
-                    if (cap > 0.0f) v0 = tt_bound(v0, cap, two_over_cap), v1 = tt_bound(v1, cap, two_over_cap);
+                for (int e = 0; e < 4; e++) {
+                    s[nb][e] *= factor[a];
+                    if (cap > 0.0f) s[nb][e] = tt_bound(s[nb][e], cap, two_over_cap);
+                }
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    const float4 v = make_float4(s[2 * half][2 * i], s[2 * half][2 * i + 1], s[2 * half + 1][2 * i], s[2 * half + 1][2 * i + 1]);
 #pragma unroll
                     for (int c = 0; c < CL; c++)
-                        *reinterpret_cast<float2*>(raw_of[c] + (size_t)h * TT_ROWS * TT_RS + (gq + 8 * i) * TT_RS + nb * 8 + 2 * tq) = make_float2(v0, v1);
+                        *reinterpret_cast<float4*>(raw_of[c] + (size_t)h * TT_ROWS * TT_RS + (gq + 8 * i) * TT_RS + tq * 8 + half * 4) = v;
                 }
         }
         sync_heads();
@@ -417,12 +425,14 @@ talk_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
                 const float f = mh[mm];
                 const float* rm = raw + (size_t)mm * TT_ROWS * TT_RS;
 #pragma unroll
-                for (int nb = 0; nb < 4; nb++)
+                for (int i = 0; i < 2; i++)
 #pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        const float2 v = *reinterpret_cast<const float2*>(rm + (gq + 8 * i) * TT_RS + nb * 8 + 2 * tq);
-                        s[nb][2 * i] = fmaf(f, v.x, s[nb][2 * i]);
-                        s[nb][2 * i + 1] = fmaf(f, v.y, s[nb][2 * i + 1]);
+                    for (int half = 0; half < 2; half++) {
+                        const float4 v = *reinterpret_cast<const float4*>(rm + (gq + 8 * i) * TT_RS + tq * 8 + half * 4);
+                        s[2 * half][2 * i] = fmaf(f, v.x, s[2 * half][2 * i]);
+                        s[2 * half][2 * i + 1] = fmaf(f, v.y, s[2 * half][2 * i + 1]);
+                        s[2 * half + 1][2 * i] = fmaf(f, v.z, s[2 * half + 1][2 * i]);
+                        s[2 * half + 1][2 * i + 1] = fmaf(f, v.w, s[2 * half + 1][2 * i + 1]);
                     }
             }
             float tmax[2] = {-INFINITY, -INFINITY};
